@@ -297,6 +297,116 @@ typedef struct vila_mega_params {
 } vila_mega_params;
 int vila_decode_mega(const vila_mega_params* p, void* stream);
 
+/* =============================================================================================
+ * Ragged-batch building blocks of decoder-only language models that keep the residual stream in
+ * fp32 (latent attention, gated linear recurrences, routed experts).  One step runs T token rows
+ * taken from several sequences: a portion of one prompt next to single decoded tokens of others.
+ * Every tensor argument carries a dtype code so the same kernels serve the bf16 serving path and
+ * a true fp32 path:  VILA_DT_BF16 / VILA_DT_F32.  Sums, norms, softmax, gates and recurrent
+ * state are always fp32.
+ * ============================================================================================= */
+#define VILA_DT_BF16 0
+#define VILA_DT_F32 1
+#define VILA_ACT_RELU2 4 /* max(z, 0)^2 */
+
+/* out[t, :] = table[ids[t], :] as fp32 (the start of the fp32 residual stream) */
+int vila_embed_rows(const void* table, int table_dtype, const int32_t* ids, float* out, int rows,
+                    int cols, void* stream);
+
+/* out[dst(r), :] = x[r, :] / sqrt(mean(x[r, :]^2) + eps) * (w + w_offset)
+ *   w_offset 1: weights stored around zero; 0: plain weights.  dst(r) = out_rows ? out_rows[r] : r
+ *   (out_rows scatters the rows into a paged pool, e.g. a latent KV cache).  w may be NULL. */
+int vila_rmsnorm_rows(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype,
+                      float w_offset, float eps, void* out, int out_dtype, int64_t ldo,
+                      const int32_t* out_rows, int rows, int cols, void* stream);
+
+/* Gated, normed residual update of the fp32 stream x [rows, cols]:
+ *   y = sum_{j < n_partials} part[r * n_partials + j, :]          (fixed order)
+ *   y = y * sigmoid(gate[r, :] + gate_bias)                        (gate == NULL: no gate)
+ *   x[r, :] += y / sqrt(mean(y^2) + eps) * (w + w_offset)          (w == NULL: no norm weight) */
+int vila_gated_norm_residual(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
+                             const void* gate, int gate_dtype, int64_t ldg, const void* gate_bias,
+                             int bias_dtype, const void* w, int w_dtype, float w_offset, float eps,
+                             int rows, int cols, void* stream);
+
+/* vila_glinear — any-shape (grouped) linear layer on the CUDA cores with fp32 accumulation:
+ *   out = act(a · w[g]^T + bias[g]) (* row_scale)
+ * mode 0 (batched): every group g sees all M rows; its A columns start at g * a_group_off and its
+ *   output columns at g * o_group_off (per-head projections); groups == 1 is a plain linear layer.
+ * mode 1 (segmented): the rows of group g are the sorted positions [seg[g], seg[g+1]) (routed experts);
+ *   position i reads A row a_rows[i] / a_row_div (a_rows NULL: i) and writes output row o_rows[i]
+ *   (NULL: i), scaled by row_scale[o_rows[i]] when row_scale is given.  M bounds seg[groups].
+ * flags: VILA_FLAG_SWIGLU as in vila_linear (out has N / 2 columns). */
+typedef struct vila_glinear_params {
+  const void* a;
+  int64_t lda;
+  const void* w;
+  int64_t ldw, w_group_stride;
+  const void* bias;
+  int64_t bias_group_stride;
+  void* out;
+  int64_t ldo;
+  int64_t a_group_off, o_group_off;
+  const int32_t* seg;
+  const int32_t* a_rows;
+  const int32_t* o_rows;
+  const float* row_scale;
+  int32_t a_dtype, w_dtype, out_dtype;
+  int32_t M, N, K, groups, mode, a_row_div, act, flags;
+} vila_glinear_params;
+int vila_glinear(const vila_glinear_params* p, void* stream);
+
+/* vila_latent_attention — causal attention of H query heads over ONE shared latent per token
+ * (keys and values are both the cached latent c_j of width R; the per-head key/value expansions
+ * are folded into the queries before and into the output after this call):
+ *   s_ij = scale * <q_i, c_j>,  j <= pos(i);   p_ij = exp(s_ij) / (sum_j exp(s_ij) + exp(sink_h))
+ *   out_i = sigmoid(gate[i, h]) * sum_j p_ij c_j
+ * sink == NULL: ordinary softmax; gate == NULL: no output gate.  The latent lives in pages of
+ * `page` tokens: token j of a sequence is row page_tables[slot * pt_stride + j / page] * page + j % page.
+ * tiles [ntiles, 4] = (first batch row, rows (<= 16), position of the first row, slot): consecutive
+ * rows of one sequence.  decode != 0 selects the one-row-per-tile kernel (all rows must be 1). */
+typedef struct vila_latent_attn_params {
+  const float* q; /* [T, H, R] */
+  const void* cache;
+  const int32_t* page_tables;
+  const int32_t* tiles;
+  const float* sink;
+  const void* gate;
+  void* out; /* [T, H, R] */
+  int64_t ldg;
+  int32_t cache_dtype, gate_dtype, out_dtype;
+  int32_t ntiles, pt_stride, H, R, page, decode;
+  float scale;
+} vila_latent_attn_params;
+int vila_latent_attention(const vila_latent_attn_params* p, void* stream);
+
+/* vila_hgrn2_scan — gated linear recurrence with the forget gate tied to the input gate, per head:
+ *   q_t = silu(zq_t),  f_t = lower + (1 - lower) * sigmoid(zf_t + f_bias)
+ *   S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T   (S: [dim, vdim] fp32),   o_t = S_t^T q_t
+ * proj holds zq | zf | v at column offsets q_off / f_off / v_off.  seqs [nseq, 4] = (first batch row,
+ * rows, position of the first row, state slot); a sequence at position 0 starts from S = 0, otherwise
+ * from state[slot]; the state after its last row is written back.  out [T, H * vdim] fp32. */
+typedef struct vila_hgrn2_params {
+  const void* proj;
+  int64_t ldp;
+  const float* f_bias;
+  const float* lower;
+  float* state; /* [slots, H, dim, vdim] */
+  const int32_t* seqs;
+  float* out;
+  int32_t proj_dtype, q_off, f_off, v_off, nseq, H, dim, vdim;
+} vila_hgrn2_params;
+int vila_hgrn2_scan(const vila_hgrn2_params* p, void* stream);
+
+/* Router of a mixture of experts: z = w_router x + bias in fp32, the `top` largest logits (ties: the
+ * lower index), weights = softmax over the chosen logits.  idx / weight are [rows, top]. */
+int vila_moe_route(const void* x, int x_dtype, int64_t ldx, const float* w_router, const float* bias,
+                   int32_t* idx, float* weight, int rows, int cols, int experts, int top, void* stream);
+/* Stable counting sort of the rows * top (token, choice) pairs by expert: seg [experts + 1] and
+ * sorted [rows * top] (pair ids = row * top + choice), for vila_glinear mode 1. */
+int vila_moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
+                   void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,7 +35,10 @@ def test_struct_layouts_match_header_field_order():
     for cname, cls in (("vila_fmha_params", _lib.FmhaParams), ("vila_gemv_params", _lib.GemvParams),
                        ("vila_decode_attn_params", _lib.DecodeAttnParams),
                        ("vila_decode_attn_split_params", _lib.DecodeAttnSplitParams),
-                       ("vila_mega_params", _lib.MegaParams)):
+                       ("vila_mega_params", _lib.MegaParams),
+                       ("vila_glinear_params", _lib.GLinearParams),
+                       ("vila_latent_attn_params", _lib.LatentAttnParams),
+                       ("vila_hgrn2_params", _lib.Hgrn2Params)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

@@ -13,5 +13,8 @@ def load(model_path=None, config=None, device="cuda", seed=0):
     from .model.loading import load_pretrained
 
     if model_path is not None:
+        from .model.registry import language_model_architecture, load_language_model
+        if language_model_architecture(model_path) is not None:  # a token-id language model
+            return load_language_model(model_path, device=device)
         return load_pretrained(model_path, device=device)
     return LlavaLlamaModel(config or nvila_8b(), device=device).init_random(seed)

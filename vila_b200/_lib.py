@@ -70,6 +70,37 @@ class MegaParams(C.Structure):
     ]
 
 
+class GLinearParams(C.Structure):
+    _fields_ = [
+        ("a", c_void_p), ("lda", c_i64), ("w", c_void_p), ("ldw", c_i64), ("w_group_stride", c_i64),
+        ("bias", c_void_p), ("bias_group_stride", c_i64), ("out", c_void_p), ("ldo", c_i64),
+        ("a_group_off", c_i64), ("o_group_off", c_i64), ("seg", c_void_p), ("a_rows", c_void_p),
+        ("o_rows", c_void_p), ("row_scale", c_void_p),
+        ("a_dtype", C.c_int32), ("w_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("M", C.c_int32), ("N", C.c_int32), ("K", C.c_int32), ("groups", C.c_int32),
+        ("mode", C.c_int32), ("a_row_div", C.c_int32), ("act", C.c_int32), ("flags", C.c_int32),
+    ]
+
+
+class LatentAttnParams(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("cache", c_void_p), ("page_tables", c_void_p), ("tiles", c_void_p),
+        ("sink", c_void_p), ("gate", c_void_p), ("out", c_void_p), ("ldg", c_i64),
+        ("cache_dtype", C.c_int32), ("gate_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("ntiles", C.c_int32), ("pt_stride", C.c_int32), ("H", C.c_int32), ("R", C.c_int32),
+        ("page", C.c_int32), ("decode", C.c_int32), ("scale", c_float),
+    ]
+
+
+class Hgrn2Params(C.Structure):
+    _fields_ = [
+        ("proj", c_void_p), ("ldp", c_i64), ("f_bias", c_void_p), ("lower", c_void_p),
+        ("state", c_void_p), ("seqs", c_void_p), ("out", c_void_p),
+        ("proj_dtype", C.c_int32), ("q_off", C.c_int32), ("f_off", C.c_int32), ("v_off", C.c_int32),
+        ("nseq", C.c_int32), ("H", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
+    ]
+
+
 # name -> argtypes; every function returns int (0 == ok) unless listed in _RESTYPES
 SIGNATURES = {
     "vila_abi_version": [],
@@ -107,6 +138,17 @@ SIGNATURES = {
     "vila_decode_attention_batch": [C.POINTER(DecodeAttnParams), c_int, c_int, c_int, c_int, c_int, c_void_p],
     "vila_decode_attention_split": [C.POINTER(DecodeAttnSplitParams), c_void_p],
     "vila_decode_mega": [C.POINTER(MegaParams), c_void_p],
+    "vila_embed_rows": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "vila_rmsnorm_rows": [c_void_p, c_int, c_i64, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_i64,
+                          c_void_p, c_int, c_int, c_void_p],
+    "vila_gated_norm_residual": [c_void_p, c_void_p, c_int, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p,
+                                 c_int, c_void_p, c_int, c_float, c_float, c_int, c_int, c_void_p],
+    "vila_glinear": [C.POINTER(GLinearParams), c_void_p],
+    "vila_latent_attention": [C.POINTER(LatentAttnParams), c_void_p],
+    "vila_hgrn2_scan": [C.POINTER(Hgrn2Params), c_void_p],
+    "vila_moe_route": [c_void_p, c_int, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                       c_int, c_void_p],
+    "vila_moe_group": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 _RESTYPES = {"vila_last_error": C.c_char_p}
 

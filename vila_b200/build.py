@@ -30,8 +30,12 @@ SOURCES = [
     "decode.cu",
     "gemv_tma.cu",
     "decode_mega.cu",
+    "ragged_lm.cu",
+    "glinear.cu",
+    "latent_attn.cu",
+    "hgrn2.cu",
 ]
-HEADERS = ["common.cuh", "kernels.h", "../../include/vila_b200.h"]
+HEADERS = ["common.cuh", "kernels.h", "dtype_any.cuh", "../../include/vila_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -76,7 +80,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(res.stderr, file=sys.stderr)
         return obj
 
-    with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
+    with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
     link = [nvcc, "-shared", "-o", str(LIB), *map(str, objs),
             "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]

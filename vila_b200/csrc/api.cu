@@ -326,4 +326,55 @@ int vila_decode_mega(const vila_mega_params* p, void* stream) {
   return vb::decode_mega(m, st(stream));
 }
 
+// ---- ragged-batch language-model blocks ------------------------------------------------------------
+int vila_embed_rows(const void* table, int table_dtype, const int32_t* ids, float* out, int rows,
+                    int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::embed_rows(table, table_dtype, ids, out, rows, cols, st(stream));
+}
+
+int vila_rmsnorm_rows(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype,
+                      float w_offset, float eps, void* out, int out_dtype, int64_t ldo,
+                      const int32_t* out_rows, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::rmsnorm_rows(x, x_dtype, ldx, w, w_dtype, w_offset, eps, out, out_dtype, ldo, out_rows,
+                          rows, cols, st(stream));
+}
+
+int vila_gated_norm_residual(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
+                             const void* gate, int gate_dtype, int64_t ldg, const void* gate_bias,
+                             int bias_dtype, const void* w, int w_dtype, float w_offset, float eps,
+                             int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::gated_norm_residual(x, part, part_dtype, ldp, n_partials, gate, gate_dtype, ldg, gate_bias,
+                                 bias_dtype, w, w_dtype, w_offset, eps, rows, cols, st(stream));
+}
+
+int vila_glinear(const vila_glinear_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::glinear(*p, st(stream));
+}
+
+int vila_latent_attention(const vila_latent_attn_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::latent_attention(*p, st(stream));
+}
+
+int vila_hgrn2_scan(const vila_hgrn2_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::hgrn2_scan(*p, st(stream));
+}
+
+int vila_moe_route(const void* x, int x_dtype, int64_t ldx, const float* w_router, const float* bias,
+                   int32_t* idx, float* weight, int rows, int cols, int experts, int top, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::moe_route(x, x_dtype, ldx, w_router, bias, idx, weight, rows, cols, experts, top, st(stream));
+}
+
+int vila_moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
+                   void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::moe_group(idx, seg, sorted, pairs, experts, st(stream));
+}
+
 }  // extern "C"

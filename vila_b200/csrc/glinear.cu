@@ -1,0 +1,164 @@
+// vila_glinear: any-shape (grouped) linear layer on the CUDA cores, fp32 accumulation.
+// It serves (a) every linear layer of the true-fp32 path, (b) shapes the tcgen05 GEMM does not
+// take (N or K not a multiple of 8), (c) per-head batched projections (latent attention: the key /
+// value expansions folded into queries and outputs) and (d) routed experts, where the rows of a
+// group are a segment of a sorted (token, choice) list read through an index and written back
+// through an index with the routing weight applied.
+// Tile: BM x 64 x 16 with 256 threads, each thread a (BM/16) x 4 block of outputs.  The summation
+// order over K is fixed and the same for every row, wherever the row sits in a tile or a batch.
+#include "../../include/vila_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+#include "dtype_any.cuh"
+
+namespace vb {
+namespace {
+
+constexpr int BN = 64, BK = 16, kThreads = 256;
+
+template <int BM>
+__global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_params p) {
+  constexpr int TM = BM / 16;
+  __shared__ float As[BK][BM + 1];
+  __shared__ __align__(16) float Ws[BK][BN];
+  __shared__ int arow_s[BM], orow_s[BM];
+  __shared__ int grp_s[2];
+  griddep_launch_dependents();
+  griddep_wait();
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  int g, m0, m_end;
+  if (p.mode == 0) {
+    g = blockIdx.z;
+    m0 = blockIdx.y * BM;
+    m_end = p.M;
+  } else {
+    if (tid == 0) {
+      int t = blockIdx.y, found = -1, start = 0;
+      for (int e = 0; e < p.groups; ++e) {
+        const int b = p.seg[e], n = p.seg[e + 1] - b, nt = (n + BM - 1) / BM;
+        if (t < nt) { found = e; start = b + t * BM; break; }
+        t -= nt;
+      }
+      grp_s[0] = found;
+      grp_s[1] = start;
+    }
+    __syncthreads();
+    g = grp_s[0];
+    if (g < 0) return;
+    m0 = grp_s[1];
+    m_end = p.seg[g + 1];
+  }
+  const int n0 = blockIdx.x * BN;
+  for (int m = tid; m < BM; m += kThreads) {
+    const int i = m0 + m;
+    int ar = -1, orow = -1;
+    if (i < m_end) {
+      ar = p.a_rows ? p.a_rows[i] / p.a_row_div : i;
+      orow = p.o_rows ? p.o_rows[i] : i;
+    }
+    arow_s[m] = ar;
+    orow_s[m] = orow;
+  }
+  __syncthreads();
+  const size_t a_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.a_group_off : 0;
+  const size_t w_base = static_cast<size_t>(g) * p.w_group_stride;
+
+  float acc[TM][4];
+#pragma unroll
+  for (int i = 0; i < TM; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int k0 = 0; k0 < p.K; k0 += BK) {
+    for (int idx = tid; idx < BM * BK; idx += kThreads) {
+      const int m = idx / BK, k = idx % BK;
+      const int ar = arow_s[m];
+      float v = 0.f;
+      if (ar >= 0 && k0 + k < p.K) v = ld_any(p.a, p.a_dtype, static_cast<size_t>(ar) * p.lda + a_col0 + k0 + k);
+      As[k][m] = v;
+    }
+    for (int idx = tid; idx < BN * BK; idx += kThreads) {
+      const int n = idx / BK, k = idx % BK;
+      float v = 0.f;
+      if (n0 + n < p.N && k0 + k < p.K)
+        v = ld_any(p.w, p.w_dtype, w_base + static_cast<size_t>(n0 + n) * p.ldw + k0 + k);
+      Ws[k][n] = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < BK; ++k) {
+      const float4 wv = *reinterpret_cast<const float4*>(&Ws[k][tx * 4]);
+#pragma unroll
+      for (int i = 0; i < TM; ++i) {
+        const float a = As[k][ty * TM + i];
+        acc[i][0] = fmaf(a, wv.x, acc[i][0]);
+        acc[i][1] = fmaf(a, wv.y, acc[i][1]);
+        acc[i][2] = fmaf(a, wv.z, acc[i][2]);
+        acc[i][3] = fmaf(a, wv.w, acc[i][3]);
+      }
+    }
+    __syncthreads();
+  }
+
+  const size_t o_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.o_group_off : 0;
+  const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int orow = orow_s[ty * TM + i];
+    if (orow < 0) continue;
+    const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      float z = acc[i][j];
+      if (p.bias && n < p.N) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
+      if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
+      else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
+      else if (p.act == VILA_ACT_GELU_TANH) {
+        z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      }
+      v[j] = z;
+    }
+    const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
+    if (swiglu) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + tx * 4 + 2 * j;
+        if (n + 1 < p.N) st_any(p.out, p.out_dtype, ob + n / 2, silu_exact_f(v[2 * j]) * v[2 * j + 1] * rs);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + tx * 4 + j;
+        if (n < p.N) st_any(p.out, p.out_dtype, ob + n, v[j] * rs);
+      }
+    }
+  }
+}
+
+}  // namespace
+
+int glinear(const vila_glinear_params& p, cudaStream_t stream) {
+  if (p.M <= 0 || p.N <= 0) return 0;
+  VB_CHECK(p.K > 0 && p.groups >= 1, "glinear: K=%d groups=%d", p.K, p.groups);
+  VB_CHECK(p.mode == 0 || (p.mode == 1 && p.seg != nullptr), "glinear: mode %d needs seg", p.mode);
+  VB_CHECK(!(p.flags & VILA_FLAG_SWIGLU) || (p.N % 2 == 0 && p.act == VILA_ACT_NONE),
+           "glinear: the SwiGLU epilogue needs an even N and no other activation");
+  VB_CHECK(p.a_rows == nullptr || p.a_row_div >= 1, "glinear: a_row_div=%d", p.a_row_div);
+  const bool small = p.M <= 16;
+  const int bm = small ? 16 : 64;
+  dim3 grid((p.N + BN - 1) / BN, 1, 1);
+  if (p.mode == 0) {
+    grid.y = (p.M + bm - 1) / bm;
+    grid.z = p.groups;
+  } else {
+    grid.y = (p.M + bm - 1) / bm + p.groups;  // upper bound of sum_g ceil(rows_g / bm)
+  }
+  VB_CHECK(grid.y <= 65535 && grid.z <= 65535, "glinear: too many tiles (M=%d groups=%d)", p.M, p.groups);
+  if (small) VB_CUDA(launch_pdl(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p));
+  else VB_CUDA(launch_pdl(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p));
+  return 0;
+}
+
+}  // namespace vb

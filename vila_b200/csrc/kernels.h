@@ -222,4 +222,27 @@ struct MegaParams {
 };
 int decode_mega(const MegaParams& p, cudaStream_t stream);
 
+// ---- ragged-batch language-model blocks (fp32 residual stream; dtype codes VILA_DT_*) -------------
+// Parameter structs are the public ones of include/vila_b200.h.
+int embed_rows(const void* table, int dt, const int32_t* ids, float* out, int rows, int cols,
+               cudaStream_t stream);
+int rmsnorm_rows(const void* x, int x_dt, int64_t ldx, const void* w, int w_dt, float w_off, float eps,
+                 void* out, int o_dt, int64_t ldo, const int32_t* out_rows, int rows, int cols,
+                 cudaStream_t stream);
+int gated_norm_residual(float* x, const void* part, int p_dt, int64_t ldp, int np, const void* gate,
+                        int g_dt, int64_t ldg, const void* gb, int b_dt, const void* w, int w_dt,
+                        float w_off, float eps, int rows, int cols, cudaStream_t stream);
+int moe_route(const void* x, int x_dt, int64_t ldx, const float* wr, const float* bias, int32_t* idx,
+              float* weight, int rows, int cols, int experts, int top, cudaStream_t stream);
+int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
+              cudaStream_t stream);
+}  // namespace vb
+struct vila_glinear_params;
+struct vila_latent_attn_params;
+struct vila_hgrn2_params;
+namespace vb {
+int glinear(const vila_glinear_params& p, cudaStream_t stream);
+int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream);
+int hgrn2_scan(const vila_hgrn2_params& p, cudaStream_t stream);
+
 }  // namespace vb

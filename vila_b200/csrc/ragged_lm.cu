@@ -1,0 +1,226 @@
+// Row-wise building blocks of ragged-batch language-model steps with an fp32 residual stream:
+// embedding gather, RMS norm (plain or zero-centred weights, optional scatter into a paged pool),
+// the gated + normed residual update, and the router / grouping kernels of routed experts.
+// All arithmetic is fp32; tensors are read and written in the dtype their code names.
+#include "../../include/vila_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+#include "dtype_any.cuh"
+
+namespace vb {
+namespace {
+
+constexpr int kRowThreads = 256;              // 8 warps, one row per warp
+constexpr int kRowsPerCta = kRowThreads / 32;
+
+__global__ void __launch_bounds__(kRowThreads)
+embed_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restrict__ ids,
+                  float* __restrict__ out, int rows, int cols) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t src = static_cast<size_t>(ids[row]) * cols;
+  float* o = out + static_cast<size_t>(row) * cols;
+  for (int c = lane_id(); c < cols; c += 32) o[c] = ld_any(table, dt, src + c);
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+rmsnorm_rows_kernel(const void* __restrict__ x, int x_dt, int64_t ldx, const void* __restrict__ w,
+                    int w_dt, float w_off, float eps, void* __restrict__ out, int o_dt, int64_t ldo,
+                    const int32_t* __restrict__ out_rows, int rows, int cols) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const size_t xb = static_cast<size_t>(row) * ldx;
+  float ss = 0.f;
+  for (int c = lane_id(); c < cols; c += 32) {
+    const float v = ld_any(x, x_dt, xb + c);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+  const size_t ob = static_cast<size_t>(out_rows ? out_rows[row] : row) * ldo;
+  for (int c = lane_id(); c < cols; c += 32) {
+    const float g = w ? ld_any(w, w_dt, c) + w_off : 1.0f;
+    st_any(out, o_dt, ob + c, ld_any(x, x_dt, xb + c) * r * g);
+  }
+}
+
+__device__ __forceinline__ float gated_value(const void* part, int p_dt, int64_t ldp, int np,
+                                             const void* gate, int g_dt, int64_t ldg,
+                                             const void* gb, int b_dt, int row, int c) {
+  float y = 0.f;
+  for (int j = 0; j < np; ++j)
+    y += ld_any(part, p_dt, (static_cast<size_t>(row) * np + j) * ldp + c);
+  if (gate) {
+    float z = ld_any(gate, g_dt, static_cast<size_t>(row) * ldg + c);
+    if (gb) z += ld_any(gb, b_dt, c);
+    y *= sigmoid_f(z);
+  }
+  return y;
+}
+
+__global__ void __launch_bounds__(kRowThreads)
+gated_norm_residual_kernel(float* __restrict__ x, const void* __restrict__ part, int p_dt, int64_t ldp,
+                           int np, const void* __restrict__ gate, int g_dt, int64_t ldg,
+                           const void* __restrict__ gb, int b_dt, const void* __restrict__ w, int w_dt,
+                           float w_off, float eps, int rows, int cols) {
+  griddep_launch_dependents();
+  griddep_wait();
+  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  float ss = 0.f;
+  for (int c = lane_id(); c < cols; c += 32) {
+    const float y = gated_value(part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, row, c);
+    ss += y * y;
+  }
+  ss = warp_sum(ss);
+  const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
+  float* xr = x + static_cast<size_t>(row) * cols;
+  for (int c = lane_id(); c < cols; c += 32) {
+    const float y = gated_value(part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, row, c);
+    const float g = w ? ld_any(w, w_dt, c) + w_off : 1.0f;
+    xr[c] += y * r * g;
+  }
+}
+
+// ---- routed experts ------------------------------------------------------------------------------
+// One warp per token: E logits (fp32 dot products over the row), then `top` rounds of arg-max.
+__global__ void __launch_bounds__(kRowThreads)
+moe_route_kernel(const void* __restrict__ x, int x_dt, int64_t ldx, const float* __restrict__ wr,
+                 const float* __restrict__ bias, int32_t* __restrict__ idx, float* __restrict__ weight,
+                 int rows, int cols, int experts, int top) {
+  extern __shared__ float z_s[];  // [kRowsPerCta][experts]
+  griddep_launch_dependents();
+  griddep_wait();
+  const int wid = threadIdx.x >> 5, lane = lane_id();
+  const int row = blockIdx.x * kRowsPerCta + wid;
+  if (row >= rows) return;
+  float* z = z_s + wid * experts;
+  const size_t xb = static_cast<size_t>(row) * ldx;
+  for (int e = 0; e < experts; ++e) {
+    const float* we = wr + static_cast<size_t>(e) * cols;
+    float s = 0.f;
+    for (int c = lane; c < cols; c += 32) s += ld_any(x, x_dt, xb + c) * we[c];
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncwarp();
+  float first = 0.f, denom = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; bi = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (j == 0) first = best;
+    const float e_j = expf(best - first);
+    denom += e_j;
+    if (lane == 0) {
+      idx[static_cast<size_t>(row) * top + j] = bi;
+      weight[static_cast<size_t>(row) * top + j] = e_j;
+      z[bi] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  if (lane == 0)
+    for (int j = 0; j < top; ++j) weight[static_cast<size_t>(row) * top + j] /= denom;
+}
+
+// Single CTA: per-expert counts, exclusive prefix, then a stable placement (pair ids stay ascending
+// inside every expert's segment) with warp ballots.
+__global__ void __launch_bounds__(1024)
+moe_group_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ seg, int32_t* __restrict__ sorted,
+                 int pairs, int experts) {
+  extern __shared__ int cnt_s[];  // [experts + 1]
+  griddep_launch_dependents();
+  griddep_wait();
+  const int wid = threadIdx.x >> 5, lane = lane_id(), nw = blockDim.x >> 5;
+  for (int e = wid; e < experts; e += nw) {
+    int n = 0;
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      n += __popc(__ballot_sync(0xffffffffu, p < pairs && idx[p] == e));
+    }
+    if (lane == 0) cnt_s[e + 1] = n;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    cnt_s[0] = 0;
+    for (int e = 0; e < experts; ++e) cnt_s[e + 1] += cnt_s[e];
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) seg[e] = cnt_s[e];
+  for (int e = wid; e < experts; e += nw) {
+    int at = cnt_s[e];
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+      const int p = p0 + lane;
+      const bool mine = p < pairs && idx[p] == e;
+      const unsigned m = __ballot_sync(0xffffffffu, mine);
+      if (mine) sorted[at + __popc(m & ((1u << lane) - 1u))] = p;
+      at += __popc(m);
+    }
+  }
+}
+
+inline int row_grid(int rows) { return (rows + kRowsPerCta - 1) / kRowsPerCta; }
+
+}  // namespace
+
+int embed_rows(const void* table, int dt, const int32_t* ids, float* out, int rows, int cols,
+               cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CUDA(launch_pdl(embed_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt,
+                     ids, out, rows, cols));
+  return 0;
+}
+
+int rmsnorm_rows(const void* x, int x_dt, int64_t ldx, const void* w, int w_dt, float w_off, float eps,
+                 void* out, int o_dt, int64_t ldo, const int32_t* out_rows, int rows, int cols,
+                 cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(cols > 0, "rmsnorm_rows: cols=%d", cols);
+  VB_CUDA(launch_pdl(rmsnorm_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x, x_dt,
+                     ldx, w, w_dt, w_off, eps, out, o_dt, ldo, out_rows, rows, cols));
+  return 0;
+}
+
+int gated_norm_residual(float* x, const void* part, int p_dt, int64_t ldp, int np, const void* gate,
+                        int g_dt, int64_t ldg, const void* gb, int b_dt, const void* w, int w_dt,
+                        float w_off, float eps, int rows, int cols, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(np >= 1 && cols > 0, "gated_norm_residual: n_partials=%d cols=%d", np, cols);
+  VB_CUDA(launch_pdl(gated_norm_residual_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x,
+                     part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, w, w_dt, w_off, eps, rows, cols));
+  return 0;
+}
+
+int moe_route(const void* x, int x_dt, int64_t ldx, const float* wr, const float* bias, int32_t* idx,
+              float* weight, int rows, int cols, int experts, int top, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  VB_CHECK(experts >= 1 && top >= 1 && top <= experts && experts <= 1024,
+           "moe_route: experts=%d top=%d", experts, top);
+  const size_t smem = sizeof(float) * kRowsPerCta * experts;
+  VB_CUDA(launch_pdl(moe_route_kernel, dim3(row_grid(rows)), dim3(kRowThreads), smem, stream, x, x_dt,
+                     ldx, wr, bias, idx, weight, rows, cols, experts, top));
+  return 0;
+}
+
+int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
+              cudaStream_t stream) {
+  VB_CHECK(experts >= 1 && experts <= 8192 && pairs >= 0, "moe_group: experts=%d pairs=%d", experts, pairs);
+  VB_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), sizeof(int) * (experts + 1), stream, idx, seg,
+                     sorted, pairs, experts));
+  return 0;
+}
+
+}  // namespace vb

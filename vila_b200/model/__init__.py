@@ -4,7 +4,9 @@ from .configuration import (LlavaConfig, Qwen2Config, SiglipVisionConfig, nvila_
 from .llava_llama import (BasicImageEncoder, BasicVideoEncoder, LlavaLlamaModel, SyntheticTokenizer,
                           TSPVideoEncoder)
 from .modeling_vila import VILAForCausalLM
+from .moronex import MoronexConfig, MoronexForCausalLM, MoronexLayerConfig
 from .projector import MultimodalProjector
+from .registry import LANGUAGE_MODELS, language_model_architecture, load_language_model
 from .qwen2 import GraphDecoder, MegaDecoder, PagedKVCache, Qwen2ForCausalLM
 from .vision import SiglipVisionModel, SiglipVisionTower
 

@@ -22,6 +22,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..sampling import pick_token
 from .configuration import Qwen2Config
 
 PAGE = 128
@@ -480,21 +481,7 @@ class Qwen2ForCausalLM(nn.Module):
                 hist = torch.tensor([ids], dtype=torch.long, device=self.device)
                 for proc in processors:
                     lg = proc(hist, lg[None])[0]
-            if sample:
-                lg = lg / max(temperature, 1e-5)
-                if top_k and top_k > 0:
-                    kth = torch.topk(lg, top_k).values[-1]
-                    lg = lg.masked_fill(lg < kth, float("-inf"))
-                probs = torch.softmax(lg, -1)
-                if top_p < 1.0:
-                    sp, si = torch.sort(probs, descending=True)
-                    cut = torch.cumsum(sp, 0) - sp > top_p
-                    sp = sp.masked_fill(cut, 0)
-                    probs = torch.zeros_like(probs).scatter(0, si, sp)
-                    probs = probs / probs.sum()
-                tok = int(torch.multinomial(probs, 1))
-            else:
-                tok = int(torch.argmax(lg))
+            tok = pick_token(lg, sample, temperature, top_k, top_p)
             ids.append(tok)
             if tok in eos_ids:
                 break

@@ -391,3 +391,182 @@ def decode_attention_batch(qkv: torch.Tensor, positions: torch.Tensor, k_pool: t
     check(_lib.load().vila_decode_attention_batch(C.byref(p), B, qkv.stride(0), out.stride(0),
                                                   page_tables.stride(0), min(32, page_tables.shape[1]),
                                                   _stream()), "vila_decode_attention_batch")
+
+
+# ---- ragged-batch language-model blocks (fp32 residual stream) -------------------------------------
+DT_BF16, DT_F32 = 0, 1
+ACT_RELU2 = 4
+_DT = {torch.bfloat16: DT_BF16, torch.float32: DT_F32}
+
+
+def _dt(t: torch.Tensor, name: str) -> int:
+    if not t.is_cuda:
+        raise RuntimeError(f"vila_b200.ops: {name} must be a CUDA tensor (no CPU fallback exists)")
+    if t.dtype not in _DT:
+        raise RuntimeError(f"vila_b200.ops: {name} must be bfloat16 or float32, got {t.dtype}")
+    return _DT[t.dtype]
+
+
+def _i32(t: Optional[torch.Tensor], name: str) -> Optional[int]:
+    if t is None:
+        return None
+    assert t.is_cuda and t.dtype == torch.int32 and t.is_contiguous(), name
+    return t.data_ptr()
+
+
+def _f32(t: Optional[torch.Tensor], name: str) -> Optional[int]:
+    if t is None:
+        return None
+    assert t.is_cuda and t.dtype == torch.float32 and t.is_contiguous(), name
+    return t.data_ptr()
+
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """fp32 rows table[ids] (ids int32 [T])."""
+    out = torch.empty(ids.numel(), table.shape[1], dtype=torch.float32, device=table.device)
+    check(_lib.load().vila_embed_rows(_p(table), _dt(table, "table"), _i32(ids, "ids"), _p(out),
+                                      ids.numel(), table.shape[1], _stream()), "vila_embed_rows")
+    return out
+
+
+def rmsnorm_rows(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, w_offset: float = 0.0,
+                 out: Optional[torch.Tensor] = None, out_dtype=None,
+                 out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [rows, cols] (row stride arbitrary) -> x / sqrt(mean(x^2) + eps) * (w + w_offset).  out_rows
+    (int32 [rows]) scatters the result rows into `out` (a paged pool viewed as [pool rows, cols])."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    rows, cols = x.shape
+    if out is None:
+        assert out_rows is None
+        out = torch.empty(rows, cols, dtype=out_dtype or x.dtype, device=x.device)
+    assert out.dim() == 2 and out.stride(1) == 1 and out.shape[1] == cols
+    check(_lib.load().vila_rmsnorm_rows(_p(x), _dt(x, "x"), x.stride(0), _p(w), _dt(w, "w") if w is not None else 0,
+                                        w_offset, eps, _p(out), _dt(out, "out"), out.stride(0),
+                                        _i32(out_rows, "out_rows"), rows, cols, _stream()), "vila_rmsnorm_rows")
+    return out
+
+
+def gated_norm_residual(x: torch.Tensor, part: torch.Tensor, *, n_partials: int = 1,
+                        gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None,
+                        w: Optional[torch.Tensor] = None, w_offset: float = 0.0, eps: float = 1e-6) -> None:
+    """x (fp32 [rows, cols], in place) += rmsnorm(sum_j part[r * n_partials + j] * sigmoid(gate + bias)) * (w + w_offset)."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    rows, cols = x.shape
+    assert part.dim() == 2 and part.stride(1) == 1 and part.shape == (rows * n_partials, cols)
+    if gate is not None:
+        assert gate.shape == (rows, cols) and gate.stride(1) == 1
+    check(_lib.load().vila_gated_norm_residual(
+        _p(x), _p(part), _dt(part, "part"), part.stride(0), n_partials,
+        _p(gate), _dt(gate, "gate") if gate is not None else 0, gate.stride(0) if gate is not None else 0,
+        _p(gate_bias), _dt(gate_bias, "gate_bias") if gate_bias is not None else 0,
+        _p(w), _dt(w, "w") if w is not None else 0, w_offset, eps, rows, cols, _stream()),
+        "vila_gated_norm_residual")
+
+
+def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None, out_dtype=None,
+            bias: Optional[torch.Tensor] = None, act: int = ACT_NONE, swiglu: bool = False,
+            groups: int = 1, a_group_off: int = 0, o_group_off: int = 0,
+            seg: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None, a_row_div: int = 1,
+            o_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
+            out_rows_total: Optional[int] = None) -> torch.Tensor:
+    """Any-shape (grouped) linear layer, fp32 accumulation on the CUDA cores (vila_glinear).
+    w [N, K] (groups == 1) or [groups, N, K].  Batched groups (seg None): group g reads the A columns
+    [g * a_group_off, + K) and writes the output columns [g * o_group_off, + N).  Segmented (seg int32
+    [groups + 1]): the rows of group g are the sorted positions seg[g]..seg[g+1]; see the header."""
+    assert a.dim() == 2 and a.stride(1) == 1
+    if w.dim() == 2:
+        w = w[None]
+    assert w.dim() == 3 and w.stride(2) == 1 and w.shape[0] == groups, (w.shape, groups)
+    N, K = w.shape[1], w.shape[2]
+    n_out = N // 2 if swiglu else N
+    M = a.shape[0] if a_rows is None else a_rows.numel()
+    if out is None:
+        cols = n_out if seg is not None or groups == 1 else o_group_off * (groups - 1) + n_out
+        out = torch.empty(out_rows_total if out_rows_total is not None else M, cols,
+                          dtype=out_dtype or a.dtype, device=a.device)
+    assert out.dim() == 2 and out.stride(1) == 1
+    p = _lib.GLinearParams()
+    p.a, p.lda = _p(a), a.stride(0)
+    p.w, p.ldw, p.w_group_stride = _p(w), w.stride(1), w.stride(0)
+    p.bias = _p(bias)
+    p.bias_group_stride = N if bias is not None and bias.numel() > N else 0
+    p.out, p.ldo = _p(out), out.stride(0)
+    p.a_group_off, p.o_group_off = a_group_off, o_group_off
+    p.seg, p.a_rows, p.o_rows = _i32(seg, "seg"), _i32(a_rows, "a_rows"), _i32(o_rows, "o_rows")
+    p.row_scale = _f32(row_scale, "row_scale")
+    p.a_dtype, p.w_dtype, p.out_dtype = _dt(a, "a"), _dt(w, "w"), _dt(out, "out")
+    if bias is not None:
+        assert bias.dtype == w.dtype
+    p.M, p.N, p.K, p.groups = M, N, K, groups
+    p.mode = 0 if seg is None else 1
+    p.a_row_div, p.act, p.flags = a_row_div, act, 1 if swiglu else 0
+    check(_lib.load().vila_glinear(C.byref(p), _stream()), "vila_glinear")
+    return out
+
+
+def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Tensor, tiles: torch.Tensor,
+                     *, heads: int, page: int, scale: float, sink: Optional[torch.Tensor] = None,
+                     gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype=None,
+                     decode: bool = False) -> torch.Tensor:
+    """q fp32 [T, heads * R] (key expansion already folded in), cache [pool rows, R], page_tables int32
+    [slots, max_pages], tiles int32 [ntiles, 4] (row0, rows, pos0, slot) -> [T, heads * R]."""
+    assert q.dtype == torch.float32 and q.is_contiguous() and q.dim() == 2
+    assert cache.dim() == 2 and cache.is_contiguous()
+    R = cache.shape[1]
+    assert q.shape[1] == heads * R
+    if out is None:
+        out = torch.empty(q.shape, dtype=out_dtype or cache.dtype, device=q.device)
+    assert out.shape == q.shape and out.is_contiguous()
+    p = _lib.LatentAttnParams()
+    p.q, p.cache, p.out = _p(q), _p(cache), _p(out)
+    p.page_tables, p.tiles = _i32(page_tables, "page_tables"), _i32(tiles, "tiles")
+    p.sink = _f32(sink, "sink")
+    p.gate = _p(gate)
+    p.ldg = gate.stride(0) if gate is not None else 0
+    p.cache_dtype, p.out_dtype = _dt(cache, "cache"), _dt(out, "out")
+    p.gate_dtype = _dt(gate, "gate") if gate is not None else 0
+    p.ntiles, p.pt_stride = tiles.shape[0], page_tables.stride(0)
+    p.H, p.R, p.page, p.decode, p.scale = heads, R, page, 1 if decode else 0, scale
+    check(_lib.load().vila_latent_attention(C.byref(p), _stream()), "vila_latent_attention")
+    return out
+
+
+def hgrn2_scan(proj: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, *, heads: int, dim: int, vdim: int,
+               q_off: int, f_off: int, v_off: int, f_bias: Optional[torch.Tensor] = None,
+               lower: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """proj [T, >= ...] holds the pre-activations of q | f | v; state fp32 [slots, heads, dim, vdim]
+    (updated in place); seqs int32 [nseq, 4] (row0, rows, pos0, slot) -> o fp32 [T, heads * vdim]."""
+    assert proj.dim() == 2 and proj.stride(1) == 1
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, vdim)
+    out = torch.empty(proj.shape[0], heads * vdim, dtype=torch.float32, device=proj.device)
+    p = _lib.Hgrn2Params()
+    p.proj, p.ldp, p.proj_dtype = _p(proj), proj.stride(0), _dt(proj, "proj")
+    p.f_bias, p.lower = _f32(f_bias, "f_bias"), _f32(lower, "lower")
+    p.state, p.seqs, p.out = _p(state), _i32(seqs, "seqs"), _p(out)
+    p.q_off, p.f_off, p.v_off = q_off, f_off, v_off
+    p.nseq, p.H, p.dim, p.vdim = seqs.shape[0], heads, dim, vdim
+    check(_lib.load().vila_hgrn2_scan(C.byref(p), _stream()), "vila_hgrn2_scan")
+    return out
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, bias: Optional[torch.Tensor], top: int):
+    """-> (idx int32 [rows, top], weight fp32 [rows, top]); router weights / bias fp32."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    rows, cols = x.shape
+    E = w_router.shape[0]
+    idx = torch.empty(rows, top, dtype=torch.int32, device=x.device)
+    wt = torch.empty(rows, top, dtype=torch.float32, device=x.device)
+    check(_lib.load().vila_moe_route(_p(x), _dt(x, "x"), x.stride(0), _f32(w_router, "w_router"),
+                                     _f32(bias, "bias"), _p(idx), _p(wt), rows, cols, E, top, _stream()),
+          "vila_moe_route")
+    return idx, wt
+
+
+def moe_group(idx: torch.Tensor, experts: int):
+    """-> (seg int32 [experts + 1], sorted int32 [pairs]): the (token, choice) pairs grouped by expert."""
+    pairs = idx.numel()
+    seg = torch.empty(experts + 1, dtype=torch.int32, device=idx.device)
+    srt = torch.empty(max(pairs, 1), dtype=torch.int32, device=idx.device)
+    check(_lib.load().vila_moe_group(_i32(idx, "idx"), _p(seg), _p(srt), pairs, experts, _stream()),
+          "vila_moe_group")
+    return seg, srt[:pairs]

@@ -234,3 +234,212 @@ def generate_batch(llm, prompts: Sequence[torch.Tensor], max_new_tokens: int, eo
                 out[owner.pop(s)] = done
                 dec.release(s)
     return [o or [] for o in out]
+
+
+# =====================================================================================================
+# Ragged-batch token engine: prompt portions and decoded tokens of several sequences in ONE step.
+# =====================================================================================================
+# The decoders above admit a request by prefilling it alone and then advance all slots one token per
+# graph replay.  Models whose per-sequence memory is more than K/V pages (a paged latent for the
+# attention layers plus a fixed-size recurrent state for the linear-recurrence layers) are served by
+# the engine below: every step is a ragged batch (any number of rows per sequence), sequences own
+# pages from the shared free list (PageAllocator, as above) and one state slot each, and both are
+# handed back on release and reused by later sequences.  The scheduler on top (generate_tokens) does
+# continuous batching with chunked prefill; the model only sees (RaggedBatch, HybridCache).
+
+import numpy as np  # noqa: E402
+
+from .sampling import pick_token  # noqa: E402
+
+LATENT_PAGE = 64
+TILE_ROWS = 16  # rows of one sequence per attention tile (vila_latent_attention)
+
+
+class RaggedBatch:
+    """Device-side description of one step.  Row t of the batch is token ids[t]; rows of one sequence
+    are consecutive.  seqs [n, 4] = (first row, rows, position of the first row, slot) per sequence;
+    tiles = the multi-row sequences cut into <= 16-row pieces, decode_tiles = the single-row ones
+    (same 4 columns); cache_rows[t] = pool row of token t in the paged caches."""
+
+    def __init__(self, ids, cache_rows, seqs, tiles, decode_tiles):
+        self.ids, self.cache_rows, self.seqs = ids, cache_rows, seqs
+        self.tiles, self.decode_tiles = tiles, decode_tiles
+        self.T = ids.numel()
+
+
+class HybridCache:
+    """Per-sequence memory of a hybrid model: for every layer that owns a latent, a paged pool
+    [pages * page, width]; for every recurrent layer a state pool [slots, heads, dim, vdim] fp32; one
+    page-table row per slot.  The geometry comes from the model (latent_widths / state_shapes)."""
+
+    def __init__(self, model, max_tokens: int, slots: int, page: int = LATENT_PAGE):
+        dev = model.device
+        self.page, self.slots = page, slots
+        self.n_pages = max(1, (max_tokens + page - 1) // page)
+        self.latent = {i: torch.zeros(self.n_pages * page, r, device=dev, dtype=model.dtype)
+                       for i, r in model.latent_widths().items()}
+        self.state = {i: torch.zeros(slots, *shape, device=dev, dtype=torch.float32)
+                      for i, shape in model.state_shapes().items()}
+        self.page_tables = torch.zeros(slots, self.n_pages, dtype=torch.int32, device=dev)
+        self.page_tables_host = np.zeros((slots, self.n_pages), dtype=np.int32)
+        self.allocator = PageAllocator(self.n_pages)
+        self.free_slots: List[int] = list(range(slots - 1, -1, -1))
+
+
+class _Sequence:
+    __slots__ = ("slot", "pages", "length")
+
+    def __init__(self, slot: int):
+        self.slot, self.pages, self.length = slot, [], 0
+
+
+class TokenEngine:
+    """Step function + cache / state manager for token-id language models (model.forward_step,
+    model.logits).  `max_tokens` bounds the tokens live sequences hold together (each rounded up to a
+    page), `slots` the number of live sequences."""
+
+    def __init__(self, model, max_tokens: int, slots: int = 4, page: int = LATENT_PAGE):
+        self.model = model
+        self.cache = HybridCache(model, max_tokens, slots, page)
+        self.seqs: Dict[object, _Sequence] = {}
+
+    # ---- sequences --------------------------------------------------------------------------------
+    def admit(self, seq_id) -> _Sequence:
+        if seq_id in self.seqs:
+            return self.seqs[seq_id]
+        if not self.cache.free_slots:
+            raise MemoryError(f"no free state slot ({self.cache.slots} live sequences)")
+        s = self.seqs[seq_id] = _Sequence(self.cache.free_slots.pop())
+        return s
+
+    def release(self, seq_id) -> None:
+        s = self.seqs.pop(seq_id, None)
+        if s is None:
+            return
+        self.cache.allocator.release(s.pages)
+        self.cache.free_slots.append(s.slot)
+
+    def length(self, seq_id) -> int:
+        return self.seqs[seq_id].length
+
+    def _reserve(self, s: _Sequence, tokens: int) -> bool:
+        c = self.cache
+        need = (tokens + c.page - 1) // c.page - len(s.pages)
+        if need <= 0:
+            return False
+        new = c.allocator.alloc(need)
+        c.page_tables_host[s.slot, len(s.pages):len(s.pages) + need] = new
+        s.pages.extend(new)
+        return True
+
+    # ---- one step -----------------------------------------------------------------------------------
+    def _build(self, entries) -> Tuple[RaggedBatch, List[int]]:
+        c, dev = self.cache, self.model.device
+        ids, rows, seqs, tiles, dec, want_rows = [], [], [], [], [], []
+        dirty, at = False, 0
+        for seq_id, tokens, want in entries:
+            n = len(tokens)
+            if n == 0:
+                continue
+            s = self.admit(seq_id)
+            dirty |= self._reserve(s, s.length + n)
+            pos = np.arange(s.length, s.length + n)
+            pages = np.asarray(s.pages, dtype=np.int64)
+            rows.append(pages[pos // c.page] * c.page + pos % c.page)
+            ids.append(np.asarray(tokens, dtype=np.int64))
+            seqs.append((at, n, s.length, s.slot))
+            if n == 1:
+                dec.append((at, 1, s.length, s.slot))
+            else:
+                for o in range(0, n, TILE_ROWS):
+                    tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, s.slot))
+            want_rows.extend(at + int(k) for k in want)
+            s.length += n
+            at += n
+        if dirty:
+            c.page_tables.copy_(torch.from_numpy(c.page_tables_host))
+        # one host->device copy for all index arrays of the step
+        parts = [np.concatenate(ids), np.concatenate(rows), np.asarray(seqs).reshape(-1),
+                 np.asarray(tiles).reshape(-1), np.asarray(dec).reshape(-1)]
+        flat = torch.from_numpy(np.concatenate(parts).astype(np.int32)).to(dev)
+        cuts = np.cumsum([0] + [p.size for p in parts])
+        v = [flat[cuts[i]:cuts[i + 1]] for i in range(len(parts))]
+        batch = RaggedBatch(v[0], v[1], v[2].view(-1, 4), v[3].view(-1, 4) if tiles else None,
+                            v[4].view(-1, 4) if dec else None)
+        return batch, want_rows
+
+    @torch.inference_mode()
+    def step(self, entries, layer_outputs: Optional[list] = None) -> Optional[torch.Tensor]:
+        """entries: (sequence id, next token ids, indices among them whose logits are wanted).  All
+        entries run as one batch on top of what earlier steps cached.  -> fp32 logits [wanted, vocab]
+        in entry / index order (None if nothing is wanted)."""
+        entries = [e for e in entries if len(e[1])]
+        if not entries:
+            return None
+        batch, want_rows = self._build(entries)
+        x = self.model.forward_step(batch, self.cache, layer_outputs)
+        if not want_rows:
+            return None
+        sel = torch.tensor(want_rows, dtype=torch.long, device=x.device)
+        return self.model.logits(x.index_select(0, sel))
+
+
+@torch.inference_mode()
+def generate_tokens(model, prompts: Sequence[Sequence[int]], max_new_tokens: int,
+                    eos_token_ids: Sequence[int] = (), *, slots: int = 4, max_tokens: Optional[int] = None,
+                    max_step_tokens: int = 2048, sample: bool = False, temperature: float = 1.0,
+                    top_k: int = 0, top_p: float = 1.0, seed: Optional[int] = None,
+                    engine: Optional[TokenEngine] = None) -> List[List[int]]:
+    """Continuous batching with chunked prefill over a TokenEngine: at most `slots` sequences live; each
+    step carries one token of every decoding sequence plus prompt portions of the others up to
+    `max_step_tokens` rows; a sequence is admitted when a slot is free and the pool can hold its prompt
+    and its whole budget; finished ones (EOS / budget) hand pages and slot to the queue.
+    -> new ids per prompt (EOS included), in prompt order."""
+    page = engine.cache.page if engine is not None else LATENT_PAGE
+
+    def pages_for(r):
+        return (len(prompts[r]) + max_new_tokens + page - 1) // page
+
+    if engine is None:
+        live = sorted((pages_for(r) for r in range(len(prompts))), reverse=True)[:slots]
+        engine = TokenEngine(model, max_tokens or max(1, sum(live)) * page, slots, page)
+    for r in range(len(prompts)):
+        if len(prompts[r]) == 0:
+            raise ValueError("empty prompt")
+        if pages_for(r) > engine.cache.n_pages:
+            raise ValueError(f"prompt {r}: {len(prompts[r])} + {max_new_tokens} tokens exceed the cache pool")
+    gen = torch.Generator(device=model.device).manual_seed(seed) if (sample and seed is not None) else None
+    eos = set(int(e) for e in eos_token_ids)
+    queue: Deque[int] = deque(range(len(prompts)))
+    live: Dict[int, dict] = {}
+    out: List[List[int]] = [[] for _ in prompts]
+    reserved = 0
+    while queue or live:
+        while queue and engine.cache.free_slots and len(live) < slots and \
+                reserved + pages_for(queue[0]) <= engine.cache.n_pages:
+            r = queue.popleft()
+            engine.admit(("gen", r))
+            live[r] = {"tokens": list(prompts[r]), "fed": 0}
+            reserved += pages_for(r)
+        budget, entries, asked = max_step_tokens, [], []
+        for r, st in sorted(live.items(), key=lambda kv: len(kv[1]["tokens"]) - kv[1]["fed"]):
+            n = min(len(st["tokens"]) - st["fed"], budget)  # decoding sequences (1 row) come first
+            if n <= 0:
+                continue
+            chunk = st["tokens"][st["fed"]:st["fed"] + n]
+            last = st["fed"] + n == len(st["tokens"])
+            entries.append((("gen", r), chunk, [n - 1] if last else []))
+            if last:
+                asked.append(r)
+            st["fed"] += n
+            budget -= n
+        logits = engine.step(entries)
+        for k, r in enumerate(asked):
+            tok = pick_token(logits[k], sample, temperature, top_k, top_p, gen)
+            out[r].append(tok)
+            live[r]["tokens"].append(tok)
+            if tok in eos or len(out[r]) >= max_new_tokens:
+                engine.release(("gen", r))
+                reserved -= pages_for(r)
+                del live[r]
+    return out
