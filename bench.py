@@ -948,6 +948,201 @@ def run_reference_gpu(args):
     print(json.dumps(line))
 
 
+# ------------------------------------------------------------------------------------------------
+# --workload hybrid_lm: the Moronex hybrid language model next to Qwen2 (the closest model of the
+# package) at equal width / depth / heads / vocabulary, random weights, bf16
+# ------------------------------------------------------------------------------------------------
+HYBRID_SIZES = {
+    "w2048": dict(width=2048, vocab=32768, heads=16, kv_rank=512, q_rank=768, dense_ff=5632, experts=32, top=4,
+                  expert_ff=704),
+    "w4096": dict(width=4096, vocab=32768, heads=32, kv_rank=512, q_rank=1536, dense_ff=11008, experts=64, top=6,
+                  expert_ff=1408),
+}
+
+
+def hybrid_lm_config(z):
+    lat = dict(heads=z["heads"], dim=128, vdim=128, kv_rank=z["kv_rank"], q_rank=z["q_rank"], scale=128 ** -0.5)
+    rec = dict(heads=z["heads"], dim=128, vdim=128)
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": {"kind": "dense", "ff": z["dense_ff"]}},
+              {"type": "hgrn2", "mixer": dict(rec), "mlp": moe}, {"type": "hgrn2", "mixer": dict(rec), "mlp": moe},
+              {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": moe}]
+    return {"architecture": "Moronex", "layers": layers, "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def hybrid_lm_block(args, peaks):
+    import torch
+
+    from vila_b200 import ops
+    from vila_b200.model import MoronexConfig, MoronexForCausalLM, Qwen2Config, Qwen2ForCausalLM
+    from vila_b200.serving import BatchedDecoder, TokenEngine
+    dev = torch.device("cuda:0")
+    ops.ensure_workspace(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=args.steps, warm=max(3, args.warmup), setup=None):
+        ts = []
+        for i in range(warm + reps):
+            if setup is not None:
+                setup()
+            flush.fill_(i & 255)     # evict L2 (126 MB) between iterations
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    S, B, CTX, NEW = 2048, 8, 1024, 32
+    tf, gbs = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    out = {}
+    t00 = time.time()
+
+    def log(msg):
+        print("[hybrid_lm %6.1fs] %s" % (time.time() - t00, msg), file=sys.stderr, flush=True)
+
+    for name, z in HYBRID_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        log("size %s: weights" % name)
+        cfgd = hybrid_lm_config(z)
+        W, H, R = z["width"], z["heads"], z["kv_rank"]
+        lm = MoronexForCausalLM(MoronexConfig.from_dict(cfgd), dev, torch.bfloat16).init_random(0, on_device=True)
+        g = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, z["vocab"], (S,), generator=g).tolist()
+        # ---- end to end through the engine -----------------------------------------------------------
+        log('engine prefill')
+        eng = TokenEngine(lm, max_tokens=B * (CTX + 4 * NEW + 64), slots=B)
+        t_pre = timed(lambda: eng.step([("p", prompt, [S - 1])]), setup=lambda: eng.release("p"))
+        eng.release("p")
+        log('engine decode')
+        for b in range(B):
+            eng.step([(b, prompt[:CTX], [])])
+        step_in = [[(b, [int(prompt[(k * 7 + b) % S])], [0]) for b in range(B)] for k in range(NEW)]
+
+        def decode_run():
+            for k in range(NEW):
+                eng.step(step_in[k])
+        t_dec = timed(decode_run, reps=3, warm=1)     # contexts grow CTX .. CTX + 4 * NEW: fits the reserve
+        for b in range(B):
+            eng.release(b)
+        # ---- Qwen2 at equal width / depth / heads / vocabulary ---------------------------------------
+        log('qwen2')
+        qc = Qwen2Config(hidden_size=W, intermediate_size=z["dense_ff"], num_hidden_layers=4, num_attention_heads=H,
+                         num_key_value_heads=4, vocab_size=z["vocab"])
+        qw = Qwen2ForCausalLM(qc, dev)
+        for prm in qw.parameters():
+            prm.data.normal_(0, 0.02)
+        for lyr in qw.model.layers:
+            lyr._qkv_w.normal_(0, 0.02); lyr._qkv_b.zero_(); lyr._gu_w.normal_(0, 0.02)
+        emb = qw.model.embed_tokens(torch.tensor(prompt, device=dev))
+
+        def q_prefill():
+            cache = qw.new_cache(S)
+            hid = qw.prefill_hidden(emb, cache)
+            return qw.logits_from_hidden(hid[-1:])
+        tq_pre = timed(q_prefill)
+        bd = BatchedDecoder(qw, slots=B, max_tokens_per_slot=CTX + 4 * NEW + 64, max_new=4 * NEW + 8)
+        bd.capture()
+        for b in range(B):
+            bd.admit(b, emb[:CTX])
+        tq_dec = timed(lambda: bd.run(NEW), reps=3, warm=1)
+        # ---- kernel against the like kernel, at this size ----------------------------------------------
+        log('kernel ledger')
+        bf = torch.bfloat16
+        led = {}
+        L0 = lm.layers[0]
+        page = eng.cache.page
+        pool = eng.cache.latent[0]
+        pt = torch.arange(eng.cache.n_pages, dtype=torch.int32, device=dev).view(1, -1).repeat(B, 1).contiguous()
+        qa = torch.randn(S, H * R, device=dev)
+        gate = torch.randn(S, H, device=dev).to(bf)
+        tiles = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
+        t = timed(lambda: ops.latent_attention(qa, pool, pt, tiles, heads=H, page=page, scale=0.088, sink=L0.sink, gate=gate))
+        fl = H * (S * (S + 1) / 2) * 4 * R
+        led["latent_attention prefill (CUDA cores, fp32 scores and weights)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        q3 = torch.randn(S, H + 8, 128, device=dev).to(bf)
+        cache = qw.new_cache(S)
+        t = timed(lambda: ops.fmha(q3[:, :H], cache.k(0), cache.v(0), B=1, Sq=S, Sk=S, causal=True, scale=0.088, page_table=cache.page_table))
+        fl = H * (S * (S + 1) / 2) * 4 * 128
+        led["qwen2 fmha prefill (tcgen05)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        dt_ = torch.tensor([(b, 1, CTX - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
+        pt2 = (torch.arange(B, device=dev, dtype=torch.int32)[:, None] * (CTX // page) + torch.arange(eng.cache.n_pages, device=dev, dtype=torch.int32)[None]) % eng.cache.n_pages
+        t = timed(lambda: ops.latent_attention(qa[:B], pool, pt2.contiguous(), dt_, heads=H, page=page, scale=0.088, sink=L0.sink, gate=gate[:B], decode=True))
+        by = B * CTX * R * 2
+        led["latent_attention decode (8 x 1024 tokens)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs,
+                                                            "note": "unique latent bytes; each of the H head CTAs re-reads them through L2"}
+        t = timed(lambda: bd._step(), reps=3, warm=1)
+        led["qwen2 batched decode step, all kernels of 4 layers (for scale)"] = {"ms": t}
+        L1 = lm.layers[1]
+        hd = H * 128
+        proj = torch.randn(S, L1.in_w.shape[0], device=dev).to(bf)
+        state = torch.zeros(B, H, 128, 128, device=dev)
+        sq = torch.tensor([[0, S, 0, 0]], dtype=torch.int32, device=dev)
+        kw = dict(heads=H, dim=128, vdim=128, q_off=0, f_off=hd, v_off=2 * hd, f_bias=L1.f_bias, lower=L1.lower)
+        t = timed(lambda: ops.hgrn2_scan(proj, state, sq, **kw))
+        by = S * 3 * hd * 2 + S * hd * 4
+        led["hgrn2_scan prefill (2048 rows, sequential in time)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs,
+                                                                      "fp32_tflops": 4 * S * hd * 128 / t / 1e9}
+        sq8 = torch.tensor([[b, 1, 5, b] for b in range(B)], dtype=torch.int32, device=dev)
+        t = timed(lambda: ops.hgrn2_scan(proj[:B], state, sq8, **kw))
+        by = B * H * 128 * 128 * 4 * 2
+        led["hgrn2_scan decode (8 sequences)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        h = torch.randn(S, W, device=dev).to(bf)
+        t = timed(lambda: lm._experts(L1, h))
+        fl = 2 * 2 * S * z["top"] * z["expert_ff"] * W
+        led["routed experts prefill: route + group + 2 grouped CUDA-core GEMMs"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        t = timed(lambda: lm._lin(lm._lin(h, L0.gu, swiglu=True), L0.down))
+        fl = 2 * 3 * S * z["dense_ff"] * W
+        led["dense SwiGLU feed-forward prefill (tcgen05, shared with qwen2)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        t = timed(lambda: lm._experts(L1, h[:B]))
+        by = 2 * min(z["experts"], B * z["top"]) * z["expert_ff"] * W * 2
+        led["routed experts decode (8 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        x = torch.randn(S, W, device=dev)
+        y = torch.randn(S, W, device=dev).to(bf)
+        gt = torch.randn(S, W, device=dev).to(bf)
+        t = timed(lambda: ops.gated_norm_residual(x, y, gate=gt, gate_bias=L0.rg1_b, w=L0.norm1b, w_offset=1.0, eps=1e-5))
+        by = S * W * (8 + 2 + 2)
+        led["gated_norm_residual (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        xb = torch.randn(S, W, device=dev).to(bf)
+        t = timed(lambda: ops.rmsnorm(xb, qw.model.norm.weight, 1e-6))
+        by = S * W * 4
+        led["qwen2 rmsnorm (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        n_lm = sum(v.numel() for v in lm.weights.values())
+        n_qw = sum(p_.numel() for p_ in qw.parameters())
+        out[name] = {
+            "moronex": {"params_m": n_lm / 1e6, "prefill_tok_s": S / t_pre * 1e3, "prefill_ms": t_pre,
+                        "decode_tok_s": B * NEW / t_dec * 1e3, "decode_ms_per_step": t_dec / NEW},
+            "qwen2": {"params_m": n_qw / 1e6, "prefill_tok_s": S / tq_pre * 1e3, "prefill_ms": tq_pre,
+                      "decode_tok_s": B * NEW / tq_dec * 1e3, "decode_ms_per_step": tq_dec / NEW},
+            "kernels": led,
+        }
+        del lm, qw, bd, eng
+        torch.cuda.empty_cache()
+    return {"workload": "hybrid_lm: 4 layers (latent attention + dense, 2 x (HGRN2 + routed experts), latent attention "
+                        "reading layer 0's latent + routed experts) vs 4 Qwen2 layers of equal width / heads / vocabulary; "
+                        "prefill: one %d-token prompt; decode: %d sequences x %d-token context, %d steps" % (S, B, CTX, NEW),
+            "dtype": "bf16", "data": "synthetic (random weights, random ids)", "l2_policy": "256 MB buffer written between timed iterations",
+            "peaks": peaks, "sizes": out}
+
+
+def run_hybrid_lm(args):
+    import torch
+    assert torch.cuda.is_available(), "bench.py --workload hybrid_lm needs a GPU"
+    peaks = read_peaks()
+    with ClockSampler(0) as cs:
+        res = hybrid_lm_block(args, peaks)
+    res["clocks"] = cs.summary()
+    from vila_b200 import _lib
+    res["gpu_launches"] = _lib.LAUNCHES
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -962,7 +1157,12 @@ def main():
     ap.add_argument("--sp-steps", type=int, default=10)
     ap.add_argument("--profile", action="store_true",
                     help="profiling aid (ncu): 1 warm-up, 8 new tokens, no extra blocks; NOT a valid bench number")
+    ap.add_argument("--sizes", default="", help="hybrid_lm: comma-separated subset of " + ",".join(HYBRID_SIZES))
+    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm"],
+                    help="headline (default): the NVILA-8B serving step; hybrid_lm: Moronex vs Qwen2 at equal size")
     args = ap.parse_args()
+    if args.workload == "hybrid_lm":
+        return run_hybrid_lm(args)
     if args.profile:
         global NEW_TOKENS
         NEW_TOKENS = 8

@@ -28,7 +28,27 @@ def main(argv=None) -> str:
     parser.add_argument("--video_max_tiles", "-vm", type=int, default=-1)
     parser.add_argument("--json-mode", action="store_true")
     parser.add_argument("--json-schema", type=str, default=None)
+    # token-id language models (config.json names a registered architecture; no tokenizer, no media)
+    parser.add_argument("--token-ids", type=str, default=None,
+                        help="prompt as comma-separated token ids; ';' separates several prompts")
+    parser.add_argument("--max-new-tokens", type=int, default=32)
+    parser.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
+    parser.add_argument("--temperature", type=float, default=0.0, help="0: greedy")
+    parser.add_argument("--top-k", type=int, default=0)
+    parser.add_argument("--top-p", type=float, default=1.0)
+    parser.add_argument("--seed", type=int, default=None)
     args = parser.parse_args(argv)
+    from vila_b200.model.registry import language_model_architecture, load_language_model
+    if language_model_architecture(args.model_path) is not None:
+        if args.token_ids is None:
+            raise SystemExit("--token-ids is required for a token-id language model")
+        prompts = [[int(t) for t in p.split(",") if t.strip()] for p in args.token_ids.split(";")]
+        lm = load_language_model(args.model_path, dtype=args.dtype)
+        out = lm.generate(prompts, max_new_tokens=args.max_new_tokens, do_sample=args.temperature > 0,
+                          temperature=args.temperature or 1.0, top_k=args.top_k, top_p=args.top_p, seed=args.seed)
+        response = ";".join(",".join(map(str, ids)) for ids in out)
+        print(response)
+        return response
     if args.lora_path is not None:
         raise NotImplementedError("LoRA checkpoints are merged offline; pass the merged --model-path")
     if not args.json_mode:

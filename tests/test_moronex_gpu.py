@@ -502,3 +502,14 @@ def test_checkpoint_round_trip_and_registry(cuda, tmp_path):
     a = TokenEngine(model, 64, 1).step([("x", toks, [19])])
     b = TokenEngine(again, 64, 1).step([("x", toks, [19])])
     assert torch.equal(a, b)
+
+
+def test_command_line_generates_ids(cuda, tmp_path, capsys):
+    from llava.cli import infer
+    cfg, model = build("narrow", F32, seed=8)
+    model.save_pretrained(tmp_path / "m")
+    prompt = tokens_for(cfg, 9, 4)
+    text = infer.main(["--model-path", str(tmp_path / "m"), "--token-ids", ",".join(map(str, prompt)),
+                       "--max-new-tokens", "5", "--dtype", "float32"])
+    assert [int(t) for t in text.split(",")] == model.generate(prompt, max_new_tokens=5)[0]
+    assert text in capsys.readouterr().out

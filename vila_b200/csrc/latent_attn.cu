@@ -25,15 +25,53 @@ __device__ __forceinline__ size_t cache_row(const int32_t* pt, int page, int j) 
   return static_cast<size_t>(pt[j / page]) * page + (j % page);
 }
 
-// thread (i = tid / 16, l = tid % 16): scores of query i for keys l and l + 16 of the block, then the
-// accumulator columns l, l + 16, ... of query i.
-template <int KK>
+// Shared-memory rows are R4 = ceil(R / 4) * 4 wide (zero padded) with a stride of R4 + 4 floats:
+// rows start 16-byte aligned and float4 reads of 8 consecutive rows hit 8 different bank groups.
+__host__ __device__ __forceinline__ int round4(int r) { return (r + 3) & ~3; }
+
+// One warp per latent row: the page-table lookup happens once per row, the row is read with 16-byte
+// loads when its width allows and widened to fp32.  Rows past nkeys and the pad columns are zero.
+__device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, const void* cache, int dt,
+                                                  const int32_t* pt, int page, int j0, int nkeys, int R) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int jj = warp; jj < BKEY; jj += nw) {
+    float* dst = Cs + jj * RS;
+    const int j = j0 + jj;
+    if (j >= nkeys) {
+      for (int k = lane; k < R4; k += 32) dst[k] = 0.f;
+      continue;
+    }
+    const size_t row = cache_row(pt, page, j);
+    if (dt == VILA_DT_BF16 && (R & 7) == 0) {
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(cache) + row * R);
+      for (int v = lane; v < (R >> 3); v += 32) {
+        const uint4 u = __ldg(src + v);
+        float4 a, b;
+        a.x = __uint_as_float(u.x << 16); a.y = __uint_as_float(u.x & 0xffff0000u);
+        a.z = __uint_as_float(u.y << 16); a.w = __uint_as_float(u.y & 0xffff0000u);
+        b.x = __uint_as_float(u.z << 16); b.y = __uint_as_float(u.z & 0xffff0000u);
+        b.z = __uint_as_float(u.w << 16); b.w = __uint_as_float(u.w & 0xffff0000u);
+        *reinterpret_cast<float4*>(dst + 8 * v) = a;
+        *reinterpret_cast<float4*>(dst + 8 * v + 4) = b;
+      }
+    } else if (dt == VILA_DT_F32 && (R & 3) == 0) {
+      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(cache) + row * R);
+      for (int v = lane; v < (R >> 2); v += 32) *reinterpret_cast<float4*>(dst + 4 * v) = __ldg(src + v);
+    } else {
+      for (int k = lane; k < R4; k += 32) dst[k] = k < R ? ld_any(cache, dt, row * R + k) : 0.f;
+    }
+  }
+}
+
+// thread (i = tid / 16, l = tid % 16): scores of query i for keys l and l + 16 of the block (float4
+// dot products), then the accumulator columns 4l .. 4l+3 (+ 64, + 128, ...) of query i.
+template <int KK4>
 __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_latent_attn_params p) {
-  extern __shared__ float sm[];
-  const int R = p.R, RS = R + 1;
-  float* Qs = sm;                 // [BQ][R]
-  float* Cs = Qs + BQ * R;        // [BKEY][R + 1]
-  float* Ps = Cs + BKEY * RS;     // [BQ][BKEY]
+  extern __shared__ __align__(16) float sm[];
+  const int R = p.R, R4 = round4(R), RS = R4 + 4;
+  float* Qs = sm;                  // [BQ][R4]
+  float* Cs = Qs + BQ * R4;        // [BKEY][RS]
+  float* Ps = Cs + BKEY * RS;      // [BQ][BKEY]
   griddep_launch_dependents();
   griddep_wait();
   const int tid = threadIdx.x, i = tid >> 4, l = tid & 15;
@@ -42,32 +80,30 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
   const int row0 = tile[0], n = tile[1], pos0 = tile[2], slot = tile[3];
   const int32_t* pt = p.page_tables + static_cast<size_t>(slot) * p.pt_stride;
   const size_t ldq = static_cast<size_t>(p.H) * R;
-  for (int idx = tid; idx < BQ * R; idx += kThreads) {
-    const int qi = idx / R, k = idx % R;
-    Qs[idx] = qi < n ? p.q[(row0 + qi) * ldq + static_cast<size_t>(h) * R + k] * p.scale : 0.f;
+  for (int idx = tid; idx < BQ * R4; idx += kThreads) {
+    const int qi = idx / R4, k = idx % R4;
+    Qs[idx] = (qi < n && k < R) ? p.q[(row0 + qi) * ldq + static_cast<size_t>(h) * R + k] * p.scale : 0.f;
   }
   float m = p.sink ? p.sink[h] : kNegBig;
   float lsum = p.sink ? 1.0f : 0.0f;
-  float acc[KK];
+  float4 acc[KK4];
 #pragma unroll
-  for (int kk = 0; kk < KK; ++kk) acc[kk] = 0.f;
+  for (int kk = 0; kk < KK4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
   const int nkeys = pos0 + n;
   const int my_last = pos0 + i;  // last visible key of query i
   for (int j0 = 0; j0 < nkeys; j0 += BKEY) {
     __syncthreads();  // Qs ready (first pass) / previous block consumed
-    for (int idx = tid; idx < BKEY * R; idx += kThreads) {
-      const int jj = idx / R, k = idx % R, j = j0 + jj;
-      Cs[jj * RS + k] = j < nkeys ? ld_any(p.cache, p.cache_dtype, cache_row(pt, p.page, j) * R + k) : 0.f;
-    }
+    load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
     float s0 = 0.f, s1 = 0.f;
-    const float* qr = Qs + i * R;
-    const float* c0 = Cs + l * RS;
-    const float* c1 = Cs + (l + 16) * RS;
-    for (int k = 0; k < R; ++k) {
-      const float qv = qr[k];
-      s0 = fmaf(qv, c0[k], s0);
-      s1 = fmaf(qv, c1[k], s1);
+    const float4* qr = reinterpret_cast<const float4*>(Qs + i * R4);
+    const float4* c0 = reinterpret_cast<const float4*>(Cs + l * RS);
+    const float4* c1 = reinterpret_cast<const float4*>(Cs + (l + 16) * RS);
+#pragma unroll 4
+    for (int k = 0; k < (R4 >> 2); ++k) {
+      const float4 qv = qr[k], a = c0[k], b = c1[k];
+      s0 = fmaf(qv.x, a.x, s0); s0 = fmaf(qv.y, a.y, s0); s0 = fmaf(qv.z, a.z, s0); s0 = fmaf(qv.w, a.w, s0);
+      s1 = fmaf(qv.x, b.x, s1); s1 = fmaf(qv.y, b.y, s1); s1 = fmaf(qv.z, b.z, s1); s1 = fmaf(qv.w, b.w, s1);
     }
     const bool v0 = i < n && j0 + l <= my_last, v1 = i < n && j0 + l + 16 <= my_last;
     s0 = v0 ? s0 : kNegBig;
@@ -88,13 +124,20 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
     __syncthreads();
     const float* pr = Ps + i * BKEY;
 #pragma unroll
-    for (int kk = 0; kk < KK; ++kk) {
-      const int k = l + 16 * kk;
-      if (k < R) {
-        float a = acc[kk] * alpha;
-#pragma unroll 8
-        for (int jj = 0; jj < BKEY; ++jj) a = fmaf(pr[jj], Cs[jj * RS + k], a);
-        acc[kk] = a;
+    for (int kk = 0; kk < KK4; ++kk) {
+      acc[kk].x *= alpha; acc[kk].y *= alpha; acc[kk].z *= alpha; acc[kk].w *= alpha;
+    }
+#pragma unroll 4
+    for (int jj = 0; jj < BKEY; ++jj) {
+      const float pj = pr[jj];
+      const float* cr = Cs + jj * RS + 4 * l;
+#pragma unroll
+      for (int kk = 0; kk < KK4; ++kk) {
+        if (4 * l + 64 * kk < R4) {
+          const float4 c = *reinterpret_cast<const float4*>(cr + 64 * kk);
+          acc[kk].x = fmaf(pj, c.x, acc[kk].x); acc[kk].y = fmaf(pj, c.y, acc[kk].y);
+          acc[kk].z = fmaf(pj, c.z, acc[kk].z); acc[kk].w = fmaf(pj, c.w, acc[kk].w);
+        }
       }
     }
   }
@@ -102,10 +145,14 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
     const size_t row = row0 + i;
     float g = 1.0f / lsum;
     if (p.gate) g *= sigmoid_f(ld_any(p.gate, p.gate_dtype, row * p.ldg + h));
+    const size_t ob = row * ldq + static_cast<size_t>(h) * R;
 #pragma unroll
-    for (int kk = 0; kk < KK; ++kk) {
-      const int k = l + 16 * kk;
-      if (k < R) st_any(p.out, p.out_dtype, row * ldq + static_cast<size_t>(h) * R + k, acc[kk] * g);
+    for (int kk = 0; kk < KK4; ++kk) {
+      const int k = 4 * l + 64 * kk;
+      const float v[4] = {acc[kk].x, acc[kk].y, acc[kk].z, acc[kk].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (k + e < R) st_any(p.out, p.out_dtype, ob + k + e, v[e] * g);
     }
   }
 }
@@ -115,11 +162,11 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
 // column k.  The G partial accumulators of a column are summed in a fixed order at the end.
 template <int KK>
 __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila_latent_attn_params p, int RP) {
-  extern __shared__ float sm[];
-  const int R = p.R, RS = R + 1;
-  float* Qs = sm;               // [R]
-  float* Cs = Qs + R;           // [BKEY][R + 1]
-  float* Ps = Cs + BKEY * RS;   // [BKEY] + alpha + (m, l)
+  extern __shared__ __align__(16) float sm[];
+  const int R = p.R, R4 = round4(R), RS = R4 + 4;
+  float* Qs = sm;               // [R4]
+  float* Cs = Qs + R4;          // [BKEY][RS]
+  float* Ps = Cs + BKEY * RS;   // [BKEY] + alpha + sum
   griddep_launch_dependents();
   griddep_wait();
   const int tid = threadIdx.x;
@@ -128,7 +175,8 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   const int row0 = tile[0], pos0 = tile[2], slot = tile[3];
   const int32_t* pt = p.page_tables + static_cast<size_t>(slot) * p.pt_stride;
   const size_t ldq = static_cast<size_t>(p.H) * R;
-  for (int k = tid; k < R; k += kThreads) Qs[k] = p.q[row0 * ldq + static_cast<size_t>(h) * R + k] * p.scale;
+  for (int k = tid; k < R4; k += kThreads)
+    Qs[k] = k < R ? p.q[row0 * ldq + static_cast<size_t>(h) * R + k] * p.scale : 0.f;
   // key groups per column; at most BKEY so that the final [G][R] exchange fits into Cs
   const int G = RP >= kThreads ? 1 : (kThreads / RP < BKEY ? kThreads / RP : BKEY);
   const int jg = RP >= kThreads ? 0 : tid / RP;
@@ -142,13 +190,17 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   const int jj_s = tid >> 3, sub = tid & 7;
   for (int j0 = 0; j0 < nkeys; j0 += BKEY) {
     __syncthreads();
-    for (int idx = tid; idx < BKEY * R; idx += kThreads) {
-      const int jj = idx / R, k = idx % R, j = j0 + jj;
-      Cs[jj * RS + k] = j < nkeys ? ld_any(p.cache, p.cache_dtype, cache_row(pt, p.page, j) * R + k) : 0.f;
-    }
+    load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
     float s = 0.f;
-    for (int k = sub; k < R; k += 8) s = fmaf(Qs[k], Cs[jj_s * RS + k], s);
+    {
+      const float4* q4 = reinterpret_cast<const float4*>(Qs);
+      const float4* c4 = reinterpret_cast<const float4*>(Cs + jj_s * RS);
+      for (int k = sub; k < (R4 >> 2); k += 8) {
+        const float4 qv = q4[k], c = c4[k];
+        s = fmaf(qv.x, c.x, s); s = fmaf(qv.y, c.y, s); s = fmaf(qv.z, c.z, s); s = fmaf(qv.w, c.w, s);
+      }
+    }
 #pragma unroll
     for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (sub == 0) Ps[jj_s] = j0 + jj_s < nkeys ? s : kNegBig;
@@ -218,7 +270,8 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   if (p.decode) {
     int rp = 1;
     while (rp < p.R) rp <<= 1;
-    const size_t smem = sizeof(float) * (p.R + BKEY * (p.R + 1) + BKEY + 2);
+    const int r4 = round4(p.R);
+    const size_t smem = sizeof(float) * (r4 + BKEY * (r4 + 4) + BKEY + 2);
     if (p.R <= 256) {
       if (set_smem(latent_attn_decode_kernel<1>, smem)) return 2;
       VB_CUDA(launch_pdl(latent_attn_decode_kernel<1>, grid, block, smem, stream, p, rp));
@@ -228,17 +281,17 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
     }
     return 0;
   }
-  const size_t smem = sizeof(float) * (BQ * p.R + BKEY * (p.R + 1) + BQ * BKEY);
+  const int r4 = round4(p.R);
+  const size_t smem = sizeof(float) * (BQ * r4 + BKEY * (r4 + 4) + BQ * BKEY);
 #define VB_LAT_TILE(KK)                                                                    \
   do {                                                                                     \
     if (set_smem(latent_attn_tile_kernel<KK>, smem)) return 2;                             \
     VB_CUDA(launch_pdl(latent_attn_tile_kernel<KK>, grid, block, smem, stream, p));        \
   } while (0)
-  if (p.R <= 32) VB_LAT_TILE(2);
-  else if (p.R <= 64) VB_LAT_TILE(4);
-  else if (p.R <= 128) VB_LAT_TILE(8);
-  else if (p.R <= 256) VB_LAT_TILE(16);
-  else VB_LAT_TILE(32);
+  if (p.R <= 64) VB_LAT_TILE(1);
+  else if (p.R <= 128) VB_LAT_TILE(2);
+  else if (p.R <= 256) VB_LAT_TILE(4);
+  else VB_LAT_TILE(8);
 #undef VB_LAT_TILE
   return 0;
 }

@@ -203,16 +203,18 @@ class MoronexForCausalLM:
             tensors.update(read_safetensors(f))
         return cls(cfg, device, dtype).load_weights(tensors)
 
-    def init_random(self, seed: int = 0, scale: float = 1.0) -> "MoronexForCausalLM":
-        g = torch.Generator().manual_seed(seed)
+    def init_random(self, seed: int = 0, scale: float = 1.0, on_device: bool = False) -> "MoronexForCausalLM":
+        """Random bf16-representable weights.  on_device: draw them on the model's device (large models)."""
+        dev = self.device if on_device else torch.device("cpu")
+        g = torch.Generator(device=dev).manual_seed(seed)
         t = {}
         for name, shape in self.config.tensor_shapes().items():
             if len(shape) == 2:
-                v = torch.randn(shape, generator=g) * (scale / shape[1] ** 0.5)
+                v = torch.randn(shape, generator=g, device=dev) * (scale / shape[1] ** 0.5)
             elif name.endswith(".lower"):
-                v = torch.rand(shape, generator=g) * 0.9
+                v = torch.rand(shape, generator=g, device=dev) * 0.9
             else:
-                v = torch.randn(shape, generator=g) * 0.1
+                v = torch.randn(shape, generator=g, device=dev) * 0.1
             t[name] = v.to(torch.bfloat16)
         return self.load_weights(t)
 
@@ -389,3 +391,16 @@ class MoronexForCausalLM:
         h = ops.rmsnorm_rows(hidden_rows.contiguous(), self.final_norm, self.config.norm_eps, w_offset=1.0,
                              out_dtype=self.dtype)
         return ops.glinear(h, self.head, out_dtype=torch.float32)
+
+    @torch.inference_mode()
+    def generate(self, input_ids, max_new_tokens: int = 20, eos_token_id=None, do_sample: bool = False,
+                 temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0, seed: Optional[int] = None,
+                 slots: int = 4, **engine_kw) -> List[List[int]]:
+        """input_ids: one prompt (list of ids) or a list of prompts -> new ids per prompt, through the
+        continuous-batching scheduler (vila_b200.serving.generate_tokens)."""
+        from ..serving import generate_tokens
+        prompts = [list(map(int, input_ids))] if input_ids and not isinstance(input_ids[0], (list, tuple)) \
+            else [list(map(int, p)) for p in input_ids]
+        eos = [] if eos_token_id is None else ([eos_token_id] if isinstance(eos_token_id, int) else list(eos_token_id))
+        return generate_tokens(self, prompts, max_new_tokens, eos, slots=slots, sample=do_sample,
+                               temperature=temperature, top_k=top_k, top_p=top_p, seed=seed, **engine_kw)
