@@ -977,7 +977,8 @@ def hybrid_lm_block(args, peaks):
     from vila_b200.model import MoronexConfig, MoronexForCausalLM, Qwen2Config, Qwen2ForCausalLM
     from vila_b200.serving import BatchedDecoder, TokenEngine
     dev = torch.device("cuda:0")
-    ops.ensure_workspace(dev)
+    if os.environ.get("VILA_BENCH_WORKSPACE", "0") == "1":
+        ops.ensure_workspace(dev)     # enables the stream-K / split-K schedules of vila_linear
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
@@ -1134,6 +1135,9 @@ def hybrid_lm_block(args, peaks):
 def run_hybrid_lm(args):
     import torch
     assert torch.cuda.is_available(), "bench.py --workload hybrid_lm needs a GPU"
+    import faulthandler
+    # a stuck run prints where it stands and ends instead of holding the GPU
+    faulthandler.dump_traceback_later(int(os.environ.get("VILA_BENCH_WATCHDOG_S", "480")), exit=True)
     peaks = read_peaks()
     with ClockSampler(0) as cs:
         res = hybrid_lm_block(args, peaks)

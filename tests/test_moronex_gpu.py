@@ -438,7 +438,8 @@ def test_mixed_batches_reuse_pages_and_slots(cuda, name, dtype):
     cfg, model = build(name, dtype, seed=4)
     prompts = {"a": tokens_for(cfg, 100, 5), "b": tokens_for(cfg, 37, 6), "c": tokens_for(cfg, 128, 7),
                "d": tokens_for(cfg, 3, 8)}
-    schedule = [[("a", 30), ("b", 2)], [("a", 1), ("b", 33)], [("b", 1), ("a", 50)], [("a", 19), ("b", 1)],
+    schedule = [[("a", 30), ("b", 2)], [("a", 1), ("b", 1)], [("a", 1), ("b", 1)], [("a", 1), ("b", 1)],   # two-row
+                [("a", 1), ("b", 30)], [("b", 1), ("a", 47)], [("a", 19), ("b", 1)],   # decode steps: eager, captured, replayed
                 [("c", 63)], [("d", 1), ("c", 2)], [("c", 1), ("d", 2)], [("c", 62)]]
     got = run_schedule(model, prompts, schedule, max_tokens=192, slots=2)
     check_logits(cfg, model, prompts, got, dtype)

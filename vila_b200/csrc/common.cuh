@@ -452,6 +452,20 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
                               cudaStream_t stream, Args... args) {
   return launch_pdl_cluster(kern, grid, block, smem, stream, dim3(1, 1, 1), args...);
 }
+// Plain stream-ordered launch (no programmatic dependent launch): the kernel starts after everything
+// before it in the stream has completed, and it never releases its successor early.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_serial(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                 cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 const char* last_error();
 
 // One-time per-DEVICE setup guard (cudaFuncSetAttribute is per device; a process may drive several).

@@ -23,8 +23,6 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
   __shared__ __align__(16) float Ws[BK][BN];
   __shared__ int arow_s[BM], orow_s[BM];
   __shared__ int grp_s[2];
-  griddep_launch_dependents();
-  griddep_wait();
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   int g, m0, m_end;
   if (p.mode == 0) {
@@ -137,6 +135,119 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
   }
 }
 
+// ---- few rows per group (decoded tokens): weight-streaming kernel ---------------------------------
+// One warp per PAIR of output columns; the lanes split K in 8-element pieces (16-byte loads of bf16
+// weights, 32-byte of fp32), every weight byte is read once per chunk of up to 16 rows, the rows of A
+// come from L1 / L2.  Serves the routed experts, the per-head folded projections and the output head
+// of decode steps, all of which are bound by the weight stream.
+constexpr int kSmallRows = 16, kSmallWarps = 8;
+
+__device__ __forceinline__ void load8(const void* p, int dt, size_t i, float (&v)[8]) {
+  if (dt) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i));
+    const float4 b = __ldg(reinterpret_cast<const float4*>(static_cast<const float*>(p) + i + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p) + i));
+    v[0] = __uint_as_float(u.x << 16); v[1] = __uint_as_float(u.x & 0xffff0000u);
+    v[2] = __uint_as_float(u.y << 16); v[3] = __uint_as_float(u.y & 0xffff0000u);
+    v[4] = __uint_as_float(u.z << 16); v[5] = __uint_as_float(u.z & 0xffff0000u);
+    v[6] = __uint_as_float(u.w << 16); v[7] = __uint_as_float(u.w & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ float finish(const vila_glinear_params& p, float z, int g, int n) {
+  if (p.bias) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
+  if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
+  else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
+  else if (p.act == VILA_ACT_GELU_TANH)
+    z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  return z;
+}
+
+// vec: K % 8 == 0 and every row of A and W starts on an 8-element boundary (16 B bf16, 32 B fp32)
+__global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const vila_glinear_params p, int vec) {
+  __shared__ int arow_s[kSmallRows], orow_s[kSmallRows];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = blockIdx.y;
+  const int n_a = (blockIdx.x * kSmallWarps + warp) * 2, n_b = n_a + 1;
+  const int m_begin = p.mode == 0 ? 0 : p.seg[g], m_end = p.mode == 0 ? p.M : p.seg[g + 1];
+  const size_t a_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.a_group_off : 0;
+  const size_t o_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.o_group_off : 0;
+  const size_t wa = static_cast<size_t>(g) * p.w_group_stride + static_cast<size_t>(n_a) * p.ldw;
+  const size_t wb = wa + p.ldw;
+  const bool has_a = n_a < p.N, has_b = n_b < p.N;
+  const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+  for (int m0 = m_begin; m0 < m_end; m0 += kSmallRows) {
+    const int nr = min(kSmallRows, m_end - m0);
+    __syncthreads();
+    if (threadIdx.x < kSmallRows) {
+      const int i = m0 + threadIdx.x;
+      const bool ok = threadIdx.x < nr;
+      arow_s[threadIdx.x] = ok ? (p.a_rows ? p.a_rows[i] / p.a_row_div : i) : 0;
+      orow_s[threadIdx.x] = ok ? (p.o_rows ? p.o_rows[i] : i) : -1;
+    }
+    __syncthreads();
+    float acc_a[kSmallRows], acc_b[kSmallRows];
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r) acc_a[r] = acc_b[r] = 0.f;
+    if (has_a) {
+      if (vec) {
+        for (int k = lane * 8; k < p.K; k += 256) {
+          float w0[8], w1[8], a[8];
+          load8(p.w, p.w_dtype, wa + k, w0);
+          if (has_b) load8(p.w, p.w_dtype, wb + k, w1);
+          else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) w1[e] = 0.f;
+          }
+#pragma unroll
+          for (int r = 0; r < kSmallRows; ++r) {
+            if (r < nr) {
+              load8(p.a, p.a_dtype, static_cast<size_t>(arow_s[r]) * p.lda + a_col0 + k, a);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                acc_a[r] = fmaf(a[e], w0[e], acc_a[r]);
+                acc_b[r] = fmaf(a[e], w1[e], acc_b[r]);
+              }
+            }
+          }
+        }
+      } else {
+        for (int k = lane; k < p.K; k += 32) {
+          const float w0 = ld_any(p.w, p.w_dtype, wa + k);
+          const float w1 = has_b ? ld_any(p.w, p.w_dtype, wb + k) : 0.f;
+#pragma unroll
+          for (int r = 0; r < kSmallRows; ++r) {
+            if (r < nr) {
+              const float a = ld_any(p.a, p.a_dtype, static_cast<size_t>(arow_s[r]) * p.lda + a_col0 + k);
+              acc_a[r] = fmaf(a, w0, acc_a[r]);
+              acc_b[r] = fmaf(a, w1, acc_b[r]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kSmallRows; ++r) {
+      if (r < nr) {   // nr is uniform over the CTA
+        const float za = warp_sum(acc_a[r]), zb = warp_sum(acc_b[r]);
+        const int orow = orow_s[r];
+        if (lane == 0 && has_a) {
+          const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
+          const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
+          if (swiglu) {
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, silu_exact_f(finish(p, za, g, n_a)) * finish(p, zb, g, n_b) * rs);
+          } else {
+            st_any(p.out, p.out_dtype, ob + n_a, finish(p, za, g, n_a) * rs);
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_b, finish(p, zb, g, n_b) * rs);
+          }
+        }
+      }
+    }
+  }
+}
+
 }  // namespace
 
 int glinear(const vila_glinear_params& p, cudaStream_t stream) {
@@ -147,6 +258,17 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
            "glinear: the SwiGLU epilogue needs an even N and no other activation");
   VB_CHECK(p.a_rows == nullptr || p.a_row_div >= 1, "glinear: a_row_div=%d", p.a_row_div);
   const bool small = p.M <= 16;
+  // few rows: stream the weights once per 16-row chunk instead of tiling
+  if ((p.mode == 0 && p.M <= kSmallRows) || (p.mode == 1 && p.M <= 4 * kSmallRows)) {
+    const size_t ea = p.a_dtype ? 4 : 2, ew = p.w_dtype ? 4 : 2;
+    const bool vec = p.K % 8 == 0 && p.lda % 8 == 0 && p.ldw % 8 == 0 && p.w_group_stride % 8 == 0 &&
+                     p.a_group_off % 8 == 0 && reinterpret_cast<uintptr_t>(p.a) % (8 * ea) == 0 &&
+                     reinterpret_cast<uintptr_t>(p.w) % (8 * ew) == 0;
+    const dim3 grid((p.N + 2 * kSmallWarps - 1) / (2 * kSmallWarps), p.groups);
+    VB_CHECK(grid.y <= 65535, "glinear: too many groups (%d)", p.groups);
+    VB_CUDA(launch_serial(glinear_small_kernel, grid, dim3(kSmallWarps * 32), 0, stream, p, vec ? 1 : 0));
+    return 0;
+  }
   const int bm = small ? 16 : 64;
   dim3 grid((p.N + BN - 1) / BN, 1, 1);
   if (p.mode == 0) {
@@ -156,8 +278,8 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
     grid.y = (p.M + bm - 1) / bm + p.groups;  // upper bound of sum_g ceil(rows_g / bm)
   }
   VB_CHECK(grid.y <= 65535 && grid.z <= 65535, "glinear: too many tiles (M=%d groups=%d)", p.M, p.groups);
-  if (small) VB_CUDA(launch_pdl(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p));
-  else VB_CUDA(launch_pdl(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p));
+  if (small) VB_CUDA(launch_serial(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p));
+  else VB_CUDA(launch_serial(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p));
   return 0;
 }
 

@@ -23,8 +23,6 @@ __global__ void __launch_bounds__(kThreads) hgrn2_scan_kernel(const vila_hgrn2_p
   float* q_s = sm;                    // [kChunk][dim]
   float* f_s = q_s + kChunk * dim;    // [kChunk][dim]
   float* v_s = f_s + kChunk * dim;    // [kChunk][kCols]
-  griddep_launch_dependents();
-  griddep_wait();
   const int tid = threadIdx.x, r = tid & 7, c = tid >> 3;
   const int* sq = p.seqs + 4 * blockIdx.x;
   const int row0 = sq[0], n = sq[1], pos0 = sq[2], slot = sq[3];
@@ -97,7 +95,7 @@ int hgrn2_scan(const vila_hgrn2_params& p, cudaStream_t stream) {
   const dim3 grid(p.nseq, p.H, (p.vdim + kCols - 1) / kCols), block(kThreads);
   VB_CHECK(grid.y <= 65535 && grid.z <= 65535, "hgrn2_scan: grid too large");
   const size_t smem = sizeof(float) * (2 * kChunk * p.dim + kChunk * kCols);
-#define VB_HGRN(KPT) VB_CUDA(launch_pdl(hgrn2_scan_kernel<KPT>, grid, block, smem, stream, p))
+#define VB_HGRN(KPT) VB_CUDA(launch_serial(hgrn2_scan_kernel<KPT>, grid, block, smem, stream, p))
   if (p.dim <= 16) VB_HGRN(2);
   else if (p.dim <= 32) VB_HGRN(4);
   else if (p.dim <= 64) VB_HGRN(8);

@@ -72,8 +72,6 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
   float* Qs = sm;                  // [BQ][R4]
   float* Cs = Qs + BQ * R4;        // [BKEY][RS]
   float* Ps = Cs + BKEY * RS;      // [BQ][BKEY]
-  griddep_launch_dependents();
-  griddep_wait();
   const int tid = threadIdx.x, i = tid >> 4, l = tid & 15;
   const int h = blockIdx.y;
   const int* tile = p.tiles + 4 * blockIdx.x;
@@ -167,8 +165,6 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   float* Qs = sm;               // [R4]
   float* Cs = Qs + R4;          // [BKEY][RS]
   float* Ps = Cs + BKEY * RS;   // [BKEY] + alpha + sum
-  griddep_launch_dependents();
-  griddep_wait();
   const int tid = threadIdx.x;
   const int h = blockIdx.y;
   const int* tile = p.tiles + 4 * blockIdx.x;
@@ -274,10 +270,10 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
     const size_t smem = sizeof(float) * (r4 + BKEY * (r4 + 4) + BKEY + 2);
     if (p.R <= 256) {
       if (set_smem(latent_attn_decode_kernel<1>, smem)) return 2;
-      VB_CUDA(launch_pdl(latent_attn_decode_kernel<1>, grid, block, smem, stream, p, rp));
+      VB_CUDA(launch_serial(latent_attn_decode_kernel<1>, grid, block, smem, stream, p, rp));
     } else {
       if (set_smem(latent_attn_decode_kernel<2>, smem)) return 2;
-      VB_CUDA(launch_pdl(latent_attn_decode_kernel<2>, grid, block, smem, stream, p, rp));
+      VB_CUDA(launch_serial(latent_attn_decode_kernel<2>, grid, block, smem, stream, p, rp));
     }
     return 0;
   }
@@ -286,7 +282,7 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
 #define VB_LAT_TILE(KK)                                                                    \
   do {                                                                                     \
     if (set_smem(latent_attn_tile_kernel<KK>, smem)) return 2;                             \
-    VB_CUDA(launch_pdl(latent_attn_tile_kernel<KK>, grid, block, smem, stream, p));        \
+    VB_CUDA(launch_serial(latent_attn_tile_kernel<KK>, grid, block, smem, stream, p));        \
   } while (0)
   if (p.R <= 64) VB_LAT_TILE(1);
   else if (p.R <= 128) VB_LAT_TILE(2);

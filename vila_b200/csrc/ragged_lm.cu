@@ -2,6 +2,10 @@
 // embedding gather, RMS norm (plain or zero-centred weights, optional scatter into a paged pool),
 // the gated + normed residual update, and the router / grouping kernels of routed experts.
 // All arithmetic is fp32; tensors are read and written in the dtype their code names.
+// These kernels (and the other ragged-batch kernels: glinear, latent_attn, hgrn2) are launched
+// stream-serialised (launch_serial), not with programmatic dependent launch: overlapping them with the
+// persistent GEMMs deadlocked in one measured configuration, so they neither start early nor release
+// their successor early.
 #include "../../include/vila_b200.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -10,14 +14,32 @@
 namespace vb {
 namespace {
 
-constexpr int kRowThreads = 256;              // 8 warps, one row per warp
+constexpr int kRowThreads = 256;
 constexpr int kRowsPerCta = kRowThreads / 32;
+constexpr int kWideCols = 512;  // rows at least this wide get a whole CTA, narrower ones a warp
+
+// TPR threads share a row: 32 = one warp (8 rows per CTA), 256 = the whole CTA.
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float* red) {
+  v = warp_sum(v);
+  if (TPR == 32) return v;
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < kRowsPerCta ? red[l] : 0.f;
+  return warp_sum(t);
+}
+template <int TPR>
+__device__ __forceinline__ int row_of() {
+  return TPR == 32 ? blockIdx.x * kRowsPerCta + (threadIdx.x >> 5) : blockIdx.x;
+}
+template <int TPR>
+__device__ __forceinline__ int col0_of() { return TPR == 32 ? (threadIdx.x & 31) : threadIdx.x; }
 
 __global__ void __launch_bounds__(kRowThreads)
 embed_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restrict__ ids,
                   float* __restrict__ out, int rows, int cols) {
-  griddep_launch_dependents();
-  griddep_wait();
   const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
   if (row >= rows) return;
   const size_t src = static_cast<size_t>(ids[row]) * cols;
@@ -25,24 +47,24 @@ embed_rows_kernel(const void* __restrict__ table, int dt, const int32_t* __restr
   for (int c = lane_id(); c < cols; c += 32) o[c] = ld_any(table, dt, src + c);
 }
 
+template <int TPR>
 __global__ void __launch_bounds__(kRowThreads)
 rmsnorm_rows_kernel(const void* __restrict__ x, int x_dt, int64_t ldx, const void* __restrict__ w,
                     int w_dt, float w_off, float eps, void* __restrict__ out, int o_dt, int64_t ldo,
                     const int32_t* __restrict__ out_rows, int rows, int cols) {
-  griddep_launch_dependents();
-  griddep_wait();
-  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  __shared__ float red[kRowsPerCta];
+  const int row = row_of<TPR>();
+  if (row >= rows) return;   // TPR == 256: uniform over the CTA
   const size_t xb = static_cast<size_t>(row) * ldx;
   float ss = 0.f;
-  for (int c = lane_id(); c < cols; c += 32) {
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
     const float v = ld_any(x, x_dt, xb + c);
     ss += v * v;
   }
-  ss = warp_sum(ss);
+  ss = row_sum<TPR>(ss, red);
   const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
   const size_t ob = static_cast<size_t>(out_rows ? out_rows[row] : row) * ldo;
-  for (int c = lane_id(); c < cols; c += 32) {
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
     const float g = w ? ld_any(w, w_dt, c) + w_off : 1.0f;
     st_any(out, o_dt, ob + c, ld_any(x, x_dt, xb + c) * r * g);
   }
@@ -62,24 +84,24 @@ __device__ __forceinline__ float gated_value(const void* part, int p_dt, int64_t
   return y;
 }
 
+template <int TPR>
 __global__ void __launch_bounds__(kRowThreads)
 gated_norm_residual_kernel(float* __restrict__ x, const void* __restrict__ part, int p_dt, int64_t ldp,
                            int np, const void* __restrict__ gate, int g_dt, int64_t ldg,
                            const void* __restrict__ gb, int b_dt, const void* __restrict__ w, int w_dt,
                            float w_off, float eps, int rows, int cols) {
-  griddep_launch_dependents();
-  griddep_wait();
-  const int row = blockIdx.x * kRowsPerCta + (threadIdx.x >> 5);
+  __shared__ float red[kRowsPerCta];
+  const int row = row_of<TPR>();
   if (row >= rows) return;
   float ss = 0.f;
-  for (int c = lane_id(); c < cols; c += 32) {
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
     const float y = gated_value(part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, row, c);
     ss += y * y;
   }
-  ss = warp_sum(ss);
+  ss = row_sum<TPR>(ss, red);
   const float r = 1.0f / sqrtf(ss / static_cast<float>(cols) + eps);
   float* xr = x + static_cast<size_t>(row) * cols;
-  for (int c = lane_id(); c < cols; c += 32) {
+  for (int c = col0_of<TPR>(); c < cols; c += TPR) {
     const float y = gated_value(part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, row, c);
     const float g = w ? ld_any(w, w_dt, c) + w_off : 1.0f;
     xr[c] += y * r * g;
@@ -87,27 +109,31 @@ gated_norm_residual_kernel(float* __restrict__ x, const void* __restrict__ part,
 }
 
 // ---- routed experts ------------------------------------------------------------------------------
-// One warp per token: E logits (fp32 dot products over the row), then `top` rounds of arg-max.
+// E logits per token (fp32 dot products over the row), then `top` rounds of arg-max.  TPR == 32: one
+// warp per token; TPR == 256 (few tokens): the 8 warps of a CTA split the experts of ONE token.
+template <int TPR>
 __global__ void __launch_bounds__(kRowThreads)
 moe_route_kernel(const void* __restrict__ x, int x_dt, int64_t ldx, const float* __restrict__ wr,
                  const float* __restrict__ bias, int32_t* __restrict__ idx, float* __restrict__ weight,
                  int rows, int cols, int experts, int top) {
-  extern __shared__ float z_s[];  // [kRowsPerCta][experts]
-  griddep_launch_dependents();
-  griddep_wait();
+  extern __shared__ float z_s[];  // TPR == 32: [kRowsPerCta][experts]; 256: [experts]
   const int wid = threadIdx.x >> 5, lane = lane_id();
-  const int row = blockIdx.x * kRowsPerCta + wid;
+  const int row = row_of<TPR>();
   if (row >= rows) return;
-  float* z = z_s + wid * experts;
+  float* z = TPR == 32 ? z_s + wid * experts : z_s;
   const size_t xb = static_cast<size_t>(row) * ldx;
-  for (int e = 0; e < experts; ++e) {
+  for (int e = (TPR == 32 ? 0 : wid); e < experts; e += (TPR == 32 ? 1 : kRowsPerCta)) {
     const float* we = wr + static_cast<size_t>(e) * cols;
     float s = 0.f;
     for (int c = lane; c < cols; c += 32) s += ld_any(x, x_dt, xb + c) * we[c];
     s = warp_sum(s);
     if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
   }
-  __syncwarp();
+  if (TPR == 32) __syncwarp();
+  else {
+    __syncthreads();
+    if (wid != 0) return;
+  }
   float first = 0.f, denom = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
@@ -142,8 +168,6 @@ __global__ void __launch_bounds__(1024)
 moe_group_kernel(const int32_t* __restrict__ idx, int32_t* __restrict__ seg, int32_t* __restrict__ sorted,
                  int pairs, int experts) {
   extern __shared__ int cnt_s[];  // [experts + 1]
-  griddep_launch_dependents();
-  griddep_wait();
   const int wid = threadIdx.x >> 5, lane = lane_id(), nw = blockDim.x >> 5;
   for (int e = wid; e < experts; e += nw) {
     int n = 0;
@@ -179,7 +203,7 @@ inline int row_grid(int rows) { return (rows + kRowsPerCta - 1) / kRowsPerCta; }
 int embed_rows(const void* table, int dt, const int32_t* ids, float* out, int rows, int cols,
                cudaStream_t stream) {
   if (rows <= 0) return 0;
-  VB_CUDA(launch_pdl(embed_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt,
+  VB_CUDA(launch_serial(embed_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, table, dt,
                      ids, out, rows, cols));
   return 0;
 }
@@ -189,8 +213,12 @@ int rmsnorm_rows(const void* x, int x_dt, int64_t ldx, const void* w, int w_dt, 
                  cudaStream_t stream) {
   if (rows <= 0) return 0;
   VB_CHECK(cols > 0, "rmsnorm_rows: cols=%d", cols);
-  VB_CUDA(launch_pdl(rmsnorm_rows_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x, x_dt,
-                     ldx, w, w_dt, w_off, eps, out, o_dt, ldo, out_rows, rows, cols));
+  if (cols >= kWideCols)
+    VB_CUDA(launch_serial(rmsnorm_rows_kernel<256>, dim3(rows), dim3(kRowThreads), 0, stream, x, x_dt, ldx, w,
+                       w_dt, w_off, eps, out, o_dt, ldo, out_rows, rows, cols));
+  else
+    VB_CUDA(launch_serial(rmsnorm_rows_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x, x_dt,
+                       ldx, w, w_dt, w_off, eps, out, o_dt, ldo, out_rows, rows, cols));
   return 0;
 }
 
@@ -199,8 +227,12 @@ int gated_norm_residual(float* x, const void* part, int p_dt, int64_t ldp, int n
                         float w_off, float eps, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0) return 0;
   VB_CHECK(np >= 1 && cols > 0, "gated_norm_residual: n_partials=%d cols=%d", np, cols);
-  VB_CUDA(launch_pdl(gated_norm_residual_kernel, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x,
-                     part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, w, w_dt, w_off, eps, rows, cols));
+  if (cols >= kWideCols)
+    VB_CUDA(launch_serial(gated_norm_residual_kernel<256>, dim3(rows), dim3(kRowThreads), 0, stream, x, part,
+                       p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, w, w_dt, w_off, eps, rows, cols));
+  else
+    VB_CUDA(launch_serial(gated_norm_residual_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads), 0, stream, x,
+                       part, p_dt, ldp, np, gate, g_dt, ldg, gb, b_dt, w, w_dt, w_off, eps, rows, cols));
   return 0;
 }
 
@@ -209,16 +241,20 @@ int moe_route(const void* x, int x_dt, int64_t ldx, const float* wr, const float
   if (rows <= 0) return 0;
   VB_CHECK(experts >= 1 && top >= 1 && top <= experts && experts <= 1024,
            "moe_route: experts=%d top=%d", experts, top);
-  const size_t smem = sizeof(float) * kRowsPerCta * experts;
-  VB_CUDA(launch_pdl(moe_route_kernel, dim3(row_grid(rows)), dim3(kRowThreads), smem, stream, x, x_dt,
-                     ldx, wr, bias, idx, weight, rows, cols, experts, top));
+  if (rows <= 1024)   // few tokens: a CTA per token, its warps split the experts
+    VB_CUDA(launch_serial(moe_route_kernel<256>, dim3(rows), dim3(kRowThreads), sizeof(float) * experts, stream,
+                       x, x_dt, ldx, wr, bias, idx, weight, rows, cols, experts, top));
+  else
+    VB_CUDA(launch_serial(moe_route_kernel<32>, dim3(row_grid(rows)), dim3(kRowThreads),
+                       sizeof(float) * kRowsPerCta * experts, stream, x, x_dt, ldx, wr, bias, idx, weight, rows,
+                       cols, experts, top));
   return 0;
 }
 
 int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
               cudaStream_t stream) {
   VB_CHECK(experts >= 1 && experts <= 8192 && pairs >= 0, "moe_group: experts=%d pairs=%d", experts, pairs);
-  VB_CUDA(launch_pdl(moe_group_kernel, dim3(1), dim3(1024), sizeof(int) * (experts + 1), stream, idx, seg,
+  VB_CUDA(launch_serial(moe_group_kernel, dim3(1), dim3(1024), sizeof(int) * (experts + 1), stream, idx, seg,
                      sorted, pairs, experts));
   return 0;
 }

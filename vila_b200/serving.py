@@ -298,10 +298,16 @@ class TokenEngine:
     model.logits).  `max_tokens` bounds the tokens live sequences hold together (each rounded up to a
     page), `slots` the number of live sequences."""
 
-    def __init__(self, model, max_tokens: int, slots: int = 4, page: int = LATENT_PAGE):
+    def __init__(self, model, max_tokens: int, slots: int = 4, page: int = LATENT_PAGE, graphs: bool = True):
         self.model = model
         self.cache = HybridCache(model, max_tokens, slots, page)
         self.seqs: Dict[object, _Sequence] = {}
+        # steps made of single decoded tokens only: one CUDA graph per row count (index arrays live in
+        # static buffers, page tables and state pools are static already); a row count is run eagerly
+        # the first time it occurs, captured the second time, replayed from then on
+        self.graphs = graphs
+        self._decode_graphs: Dict[int, tuple] = {}
+        self._decode_seen: Dict[int, int] = {}
 
     # ---- sequences --------------------------------------------------------------------------------
     def admit(self, seq_id) -> _Sequence:
@@ -333,7 +339,7 @@ class TokenEngine:
         return True
 
     # ---- one step -----------------------------------------------------------------------------------
-    def _build(self, entries) -> Tuple[RaggedBatch, List[int]]:
+    def _build(self, entries):
         c, dev = self.cache, self.model.device
         ids, rows, seqs, tiles, dec, want_rows = [], [], [], [], [], []
         dirty, at = False, 0
@@ -361,12 +367,35 @@ class TokenEngine:
         # one host->device copy for all index arrays of the step
         parts = [np.concatenate(ids), np.concatenate(rows), np.asarray(seqs).reshape(-1),
                  np.asarray(tiles).reshape(-1), np.asarray(dec).reshape(-1)]
-        flat = torch.from_numpy(np.concatenate(parts).astype(np.int32)).to(dev)
-        cuts = np.cumsum([0] + [p.size for p in parts])
-        v = [flat[cuts[i]:cuts[i + 1]] for i in range(len(parts))]
-        batch = RaggedBatch(v[0], v[1], v[2].view(-1, 4), v[3].view(-1, 4) if tiles else None,
-                            v[4].view(-1, 4) if dec else None)
-        return batch, want_rows
+        flat = torch.from_numpy(np.concatenate(parts).astype(np.int32))
+        return flat, [p.size for p in parts], want_rows
+
+    @staticmethod
+    def _views(flat: torch.Tensor, sizes) -> RaggedBatch:
+        cuts = np.cumsum([0] + list(sizes))
+        v = [flat[cuts[i]:cuts[i + 1]] for i in range(len(sizes))]
+        return RaggedBatch(v[0], v[1], v[2].view(-1, 4), v[3].view(-1, 4) if sizes[3] else None,
+                           v[4].view(-1, 4) if sizes[4] else None)
+
+    def _decode_step_graphed(self, flat, sizes) -> Tuple[torch.Tensor, torch.Tensor]:
+        """All rows are single decoded tokens: replay (or capture) the graph of this row count.
+        -> (residual rows, logits of ALL rows); both are static graph outputs."""
+        T = sizes[0]
+        ent = self._decode_graphs.get(T)
+        if ent is None:
+            static = torch.empty(flat.numel(), dtype=torch.int32, device=self.model.device)
+            static.copy_(flat)
+            batch = self._views(static, sizes)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                x = self.model.forward_step(batch, self.cache)
+                lg = self.model.logits(x)
+            ent = self._decode_graphs[T] = (g, static, x, lg)
+        g, static, x, lg = ent
+        static.copy_(flat)
+        g.replay()
+        return x, lg
 
     @torch.inference_mode()
     def step(self, entries, layer_outputs: Optional[list] = None) -> Optional[torch.Tensor]:
@@ -376,8 +405,18 @@ class TokenEngine:
         entries = [e for e in entries if len(e[1])]
         if not entries:
             return None
-        batch, want_rows = self._build(entries)
-        x = self.model.forward_step(batch, self.cache, layer_outputs)
+        flat, sizes, want_rows = self._build(entries)
+        T = sizes[0]
+        decode_only = sizes[3] == 0 and layer_outputs is None
+        if self.graphs and decode_only and self._decode_seen.get(T, 0) >= 1:
+            x, all_logits = self._decode_step_graphed(flat, sizes)
+            if not want_rows:
+                return None
+            sel = torch.tensor(want_rows, dtype=torch.long, device=x.device)
+            return all_logits.index_select(0, sel)
+        if decode_only:
+            self._decode_seen[T] = self._decode_seen.get(T, 0) + 1
+        x = self.model.forward_step(self._views(flat.to(self.model.device), sizes), self.cache, layer_outputs)
         if not want_rows:
             return None
         sel = torch.tensor(want_rows, dtype=torch.long, device=x.device)
