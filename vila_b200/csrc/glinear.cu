@@ -11,20 +11,62 @@
 #include "kernels.h"
 #include "dtype_any.cuh"
 
+#include <mma.h>
+
 namespace vb {
 namespace {
 
 constexpr int BN = 64, BK = 16, kThreads = 256;
 
+// Epilogue of a thread's TM x 4 block: bias, activation (or SwiGLU over column pairs), routing weight,
+// scatter through the output row index.
+template <int TM>
+__device__ __forceinline__ void store_block(const vila_glinear_params& p, int g, int n0, int tx,
+                                            const int* orows, float (&acc)[TM][4]) {
+  const size_t o_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.o_group_off : 0;
+  const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+#pragma unroll
+  for (int i = 0; i < TM; ++i) {
+    const int orow = orows[i];
+    if (orow < 0) continue;
+    const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      float z = acc[i][j];
+      if (p.bias && n < p.N) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
+      if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
+      else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
+      else if (p.act == VILA_ACT_GELU_TANH) {
+        z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+      }
+      v[j] = z;
+    }
+    const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
+    if (swiglu) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + tx * 4 + 2 * j;
+        if (n + 1 < p.N) st_any(p.out, p.out_dtype, ob + n / 2, silu_exact_f(v[2 * j]) * v[2 * j + 1] * rs);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int n = n0 + tx * 4 + j;
+        if (n < p.N) st_any(p.out, p.out_dtype, ob + n, v[j] * rs);
+      }
+    }
+  }
+}
+
+// Which rows does this CTA own?  mode 0: tile blockIdx.y of group blockIdx.z; mode 1: blockIdx.y counts
+// the BM-row tiles of all groups in order.  Fills the A-row / output-row tables; false: no work.
 template <int BM>
-__global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_params p) {
-  constexpr int TM = BM / 16;
-  __shared__ float As[BK][BM + 1];
-  __shared__ __align__(16) float Ws[BK][BN];
-  __shared__ int arow_s[BM], orow_s[BM];
-  __shared__ int grp_s[2];
-  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  int g, m0, m_end;
+__device__ __forceinline__ bool tile_rows(const vila_glinear_params& p, int* arow_s, int* orow_s, int* grp_s,
+                                          int& g) {
+  const int tid = threadIdx.x;
+  int m0, m_end;
   if (p.mode == 0) {
     g = blockIdx.z;
     m0 = blockIdx.y * BM;
@@ -42,12 +84,11 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
     }
     __syncthreads();
     g = grp_s[0];
-    if (g < 0) return;
+    if (g < 0) return false;
     m0 = grp_s[1];
     m_end = p.seg[g + 1];
   }
-  const int n0 = blockIdx.x * BN;
-  for (int m = tid; m < BM; m += kThreads) {
+  for (int m = tid; m < BM; m += blockDim.x) {
     const int i = m0 + m;
     int ar = -1, orow = -1;
     if (i < m_end) {
@@ -58,6 +99,20 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
     orow_s[m] = orow;
   }
   __syncthreads();
+  return true;
+}
+
+template <int BM>
+__global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_params p) {
+  constexpr int TM = BM / 16;
+  __shared__ float As[BK][BM + 1];
+  __shared__ __align__(16) float Ws[BK][BN];
+  __shared__ int arow_s[BM], orow_s[BM];
+  __shared__ int grp_s[2];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  int g;
+  if (!tile_rows<BM>(p, arow_s, orow_s, grp_s, g)) return;
+  const int n0 = blockIdx.x * BN;
   const size_t a_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.a_group_off : 0;
   const size_t w_base = static_cast<size_t>(g) * p.w_group_stride;
 
@@ -98,41 +153,78 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
     __syncthreads();
   }
 
-  const size_t o_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.o_group_off : 0;
-  const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+  store_block<TM>(p, g, n0, tx, orow_s + ty * TM, acc);
+}
+
+// ---- bf16 operands, many rows: warp-level tensor-core tiles (wmma, fp32 accumulators) ---------------
+// Same tiling contract as glinear_kernel<64> (64 x 64 outputs per CTA, groups, row gather / scatter,
+// epilogues); 8 warps as 4 x 2, each 16 x 32 outputs; K in steps of 32 through shared memory.  The
+// accumulators go through shared memory once so that the epilogue is the shared one.
+constexpr int WK = 32, WLD = WK + 8;
+
+__device__ __forceinline__ uint4 load8_bf16(const __nv_bfloat16* base, size_t off, int k, int K, bool row_ok,
+                                            bool vec) {
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (!row_ok || k >= K) return v;
+  if (vec) return __ldg(reinterpret_cast<const uint4*>(base + off + k));
+  __nv_bfloat16 t[8];
 #pragma unroll
-  for (int i = 0; i < TM; ++i) {
-    const int orow = orow_s[ty * TM + i];
-    if (orow < 0) continue;
-    const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
-    float v[4];
+  for (int e = 0; e < 8; ++e) t[e] = k + e < K ? base[off + k + e] : __float2bfloat16_rn(0.f);
+  return *reinterpret_cast<uint4*>(t);
+}
+
+__global__ void __launch_bounds__(kThreads) glinear_wmma_kernel(const vila_glinear_params p, int vec) {
+  using namespace nvcuda;
+  constexpr int BM = 64;
+  __shared__ __align__(32) __nv_bfloat16 As[BM][WLD];
+  __shared__ __align__(32) __nv_bfloat16 Ws[BN][WLD];
+  __shared__ __align__(32) float Cs[BM][BN + 4];
+  __shared__ int arow_s[BM], orow_s[BM];
+  __shared__ int grp_s[2];
+  const int tid = threadIdx.x, warp = tid >> 5;
+  int g;
+  if (!tile_rows<BM>(p, arow_s, orow_s, grp_s, g)) return;
+  const int n0 = blockIdx.x * BN;
+  const size_t a_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.a_group_off : 0;
+  const size_t w_base = static_cast<size_t>(g) * p.w_group_stride;
+  const __nv_bfloat16* A = static_cast<const __nv_bfloat16*>(p.a);
+  const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(p.w);
+  const int wm = warp & 3, wn = warp >> 2;
+  wmma::fragment<wmma::accumulator, 16, 16, 16, float> c[2];
+  wmma::fill_fragment(c[0], 0.f);
+  wmma::fill_fragment(c[1], 0.f);
+  const int lr = tid >> 2, lk = (tid & 3) * 8;   // this thread stages 8 elements of row lr
+  const int ar = arow_s[lr];
+  const bool w_ok = n0 + lr < p.N;
+  const size_t a_off = static_cast<size_t>(ar < 0 ? 0 : ar) * p.lda + a_col0;
+  const size_t w_off = w_base + static_cast<size_t>(n0 + lr) * p.ldw;
+  for (int k0 = 0; k0 < p.K; k0 += WK) {
+    *reinterpret_cast<uint4*>(&As[lr][lk]) = load8_bf16(A, a_off, k0 + lk, p.K, ar >= 0, vec);
+    *reinterpret_cast<uint4*>(&Ws[lr][lk]) = load8_bf16(W, w_off, k0 + lk, p.K, w_ok, vec);
+    __syncthreads();
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = n0 + tx * 4 + j;
-      float z = acc[i][j];
-      if (p.bias && n < p.N) z += ld_any(p.bias, p.w_dtype, static_cast<size_t>(g) * p.bias_group_stride + n);
-      if (p.act == VILA_ACT_SILU) z = silu_exact_f(z);
-      else if (p.act == VILA_ACT_RELU2) { z = fmaxf(z, 0.f); z = z * z; }
-      else if (p.act == VILA_ACT_GELU_TANH) {
-        z = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-      }
-      v[j] = z;
-    }
-    const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
-    if (swiglu) {
+    for (int kk = 0; kk < WK; kk += 16) {
+      wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+      wmma::load_matrix_sync(fa, &As[wm * 16][kk], WLD);
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int n = n0 + tx * 4 + 2 * j;
-        if (n + 1 < p.N) st_any(p.out, p.out_dtype, ob + n / 2, silu_exact_f(v[2 * j]) * v[2 * j + 1] * rs);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int n = n0 + tx * 4 + j;
-        if (n < p.N) st_any(p.out, p.out_dtype, ob + n, v[j] * rs);
+        wmma::fragment<wmma::matrix_b, 16, 16, 16, __nv_bfloat16, wmma::col_major> fb;
+        wmma::load_matrix_sync(fb, &Ws[wn * 32 + j * 16][kk], WLD);
+        wmma::mma_sync(c[j], fa, fb, c[j]);
       }
     }
+    __syncthreads();
   }
+  wmma::store_matrix_sync(&Cs[wm * 16][wn * 32], c[0], BN + 4, wmma::mem_row_major);
+  wmma::store_matrix_sync(&Cs[wm * 16][wn * 32 + 16], c[1], BN + 4, wmma::mem_row_major);
+  __syncthreads();
+  const int tx = tid & 15, ty = tid >> 4;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = Cs[ty * 4 + i][tx * 4 + j];
+  store_block<4>(p, g, n0, tx, orow_s + ty * 4, acc);
 }
 
 // ---- few rows per group (decoded tokens): weight-streaming kernel ---------------------------------
@@ -278,6 +370,15 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
     grid.y = (p.M + bm - 1) / bm + p.groups;  // upper bound of sum_g ceil(rows_g / bm)
   }
   VB_CHECK(grid.y <= 65535 && grid.z <= 65535, "glinear: too many tiles (M=%d groups=%d)", p.M, p.groups);
+  if (!small && p.a_dtype == VILA_DT_BF16 && p.w_dtype == VILA_DT_BF16) {
+    // bf16 operands: tensor-core tiles.  16-byte loads need every row of A and W to start on an
+    // 8-element boundary; otherwise the same kernel stages element by element.
+    const bool vec = p.K % 8 == 0 && p.lda % 8 == 0 && p.ldw % 8 == 0 && p.w_group_stride % 8 == 0 &&
+                     p.a_group_off % 8 == 0 && reinterpret_cast<uintptr_t>(p.a) % 16 == 0 &&
+                     reinterpret_cast<uintptr_t>(p.w) % 16 == 0;
+    VB_CUDA(launch_serial(glinear_wmma_kernel, grid, dim3(kThreads), 0, stream, p, vec ? 1 : 0));
+    return 0;
+  }
   if (small) VB_CUDA(launch_serial(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p));
   else VB_CUDA(launch_serial(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p));
   return 0;
