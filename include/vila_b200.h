@@ -407,6 +407,32 @@ int vila_moe_route(const void* x, int x_dtype, int64_t ldx, const float* w_route
 int vila_moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
                    void* stream);
 
+/* dst[i, :] = src[rows[i], :] for rows of row_bytes bytes (any dtype; 16-byte copies when row_bytes and
+ * both bases allow).  Used to lay the cached latents of a sequence out contiguously. */
+int vila_gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes,
+                     void* stream);
+
+/* vila_sink_attention — causal multi-head attention with separate keys and values, fp32 scores /
+ * softmax / weighted sum, optional per-head sink in the denominator and sigmoid output gate (as
+ * vila_latent_attention).  k / v hold, for every sequence of the launch, the rows of ALL its positions
+ * 0 .. pos0 + rows - 1, contiguously from row kv_row0: head h of position j at
+ * k[(kv_row0 + j) * ldk + h * dim], v[(kv_row0 + j) * ldv + h * vdim].
+ * tiles [ntiles, 4] = (first batch row, rows (<= 16), position of the first row, kv_row0). */
+typedef struct vila_sink_attn_params {
+  const void* q; /* [T, H * dim] */
+  const void* k;
+  const void* v;
+  const int32_t* tiles;
+  const float* sink;
+  const void* gate;
+  void* out; /* [T, H * vdim] */
+  int64_t ldq, ldk, ldv, ldg, ldo;
+  int32_t q_dtype, kv_dtype, gate_dtype, out_dtype;
+  int32_t ntiles, H, dim, vdim;
+  float scale;
+} vila_sink_attn_params;
+int vila_sink_attention(const vila_sink_attn_params* p, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

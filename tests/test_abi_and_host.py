@@ -38,7 +38,8 @@ def test_struct_layouts_match_header_field_order():
                        ("vila_mega_params", _lib.MegaParams),
                        ("vila_glinear_params", _lib.GLinearParams),
                        ("vila_latent_attn_params", _lib.LatentAttnParams),
-                       ("vila_hgrn2_params", _lib.Hgrn2Params)):
+                       ("vila_hgrn2_params", _lib.Hgrn2Params),
+                       ("vila_sink_attn_params", _lib.SinkAttnParams)):
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, flags=re.S).group(1)
         body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
         fields = []

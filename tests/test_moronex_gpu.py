@@ -514,3 +514,54 @@ def test_command_line_generates_ids(cuda, tmp_path, capsys):
                        "--max-new-tokens", "5", "--dtype", "float32"])
     assert [int(t) for t in text.split(",")] == model.generate(prompt, max_new_tokens=5)[0]
     assert text in capsys.readouterr().out
+
+
+@pytest.mark.parametrize("dtype", [F32, BF])
+@pytest.mark.parametrize("H,dim,vdim", [(3, 24, 40), (2, 128, 128), (1, 10, 300)])
+def test_sink_attention_and_gather_rows(cuda, dtype, H, dim, vdim):
+    """The un-folded kernel: keys / values as strided views of one buffer, two sequences (one continuing
+    at position 150, one from 0), tiles that end at ragged sizes; gather_rows feeds it in the model."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(dim)
+    src = torch.randn(50, 12, generator=g).to(dtype).cuda()
+    pick = torch.randperm(50, generator=g)[:23].to(torch.int32).cuda()
+    assert torch.equal(ops.gather_rows(src, pick), src[pick.long()])
+    lens, news = [200, 37], [50, 37]
+    kv = torch.randn(sum(lens), H * (dim + vdim) + 8, generator=g).to(dtype)
+    k, v = kv[:, :H * dim], kv[:, H * dim + 8:]
+    T = sum(news)
+    q = torch.randn(T, H * dim, generator=g).to(dtype)
+    gate, sink = torch.randn(T, H, generator=g).to(dtype), torch.randn(H, generator=g)
+    tiles, want, at, kv0 = [], torch.zeros(T, H, vdim, dtype=torch.float64), 0, 0
+    for L, n in zip(lens, news):
+        p0 = L - n
+        for o in range(0, n, 16):
+            tiles.append((at + o, min(16, n - o), p0 + o, kv0))
+        for i in range(n):
+            for h in range(H):
+                ks = k[kv0:kv0 + p0 + i + 1, h * dim:(h + 1) * dim].double()
+                vs = v[kv0:kv0 + p0 + i + 1, h * vdim:(h + 1) * vdim].double()
+                s = ks @ q[at + i, h * dim:(h + 1) * dim].double() * 0.3
+                m = max(float(s.max()), float(sink[h]))
+                e = torch.exp(s - m)
+                o_ = (e[:, None] * vs).sum(0) / (e.sum() + math.exp(float(sink[h]) - m))
+                want[at + i, h] = o_ * torch.sigmoid(gate[at + i, h].double())
+        at += n
+        kv0 += L
+    kvd = kv.cuda()
+    got = ops.sink_attention(q.cuda(), kvd[:, :H * dim], kvd[:, H * dim + 8:], torch.tensor(tiles, dtype=torch.int32).cuda(),
+                             heads=H, scale=0.3, sink=sink.cuda(), gate=gate.cuda(), out_dtype=F32)
+    assert rel(got.view(T, H, vdim), want) < (1e-5 if dtype == F32 else 1e-2)
+
+
+@pytest.mark.parametrize("ratio", [0, 4])
+def test_folded_and_unfolded_attention_agree(cuda, ratio):
+    """The same prompt through the folded form only (ratio 0) and with the un-folded form for large
+    portions, in fp32: both against the oracle."""
+    from vila_b200.serving import TokenEngine
+    cfg, model = build("odd", F32, seed=9)
+    toks = tokens_for(cfg, 120, 11)
+    eng = TokenEngine(model, max_tokens=128, slots=1)
+    eng.unfold_ratio = ratio
+    got = torch.cat([eng.step([("s", toks[a:b], list(range(b - a)))]).cpu() for a, b in ((0, 70), (70, 73), (73, 120))])
+    rows_close(got, O.forward(cfg, model.state_dict(), toks)[0], F32, f"ratio {ratio}")

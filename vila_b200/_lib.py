@@ -92,6 +92,16 @@ class LatentAttnParams(C.Structure):
     ]
 
 
+class SinkAttnParams(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("tiles", c_void_p), ("sink", c_void_p),
+        ("gate", c_void_p), ("out", c_void_p),
+        ("ldq", c_i64), ("ldk", c_i64), ("ldv", c_i64), ("ldg", c_i64), ("ldo", c_i64),
+        ("q_dtype", C.c_int32), ("kv_dtype", C.c_int32), ("gate_dtype", C.c_int32), ("out_dtype", C.c_int32),
+        ("ntiles", C.c_int32), ("H", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("scale", c_float),
+    ]
+
+
 class Hgrn2Params(C.Structure):
     _fields_ = [
         ("proj", c_void_p), ("ldp", c_i64), ("f_bias", c_void_p), ("lower", c_void_p),
@@ -146,6 +156,8 @@ SIGNATURES = {
     "vila_glinear": [C.POINTER(GLinearParams), c_void_p],
     "vila_latent_attention": [C.POINTER(LatentAttnParams), c_void_p],
     "vila_hgrn2_scan": [C.POINTER(Hgrn2Params), c_void_p],
+    "vila_sink_attention": [C.POINTER(SinkAttnParams), c_void_p],
+    "vila_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "vila_moe_route": [c_void_p, c_int, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                        c_int, c_void_p],
     "vila_moe_group": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -360,6 +360,17 @@ int vila_latent_attention(const vila_latent_attn_params* p, void* stream) {
   return vb::latent_attention(*p, st(stream));
 }
 
+int vila_sink_attention(const vila_sink_attn_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::sink_attention(*p, st(stream));
+}
+
+int vila_gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes,
+                     void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::gather_rows(src, rows, dst, n_rows, row_bytes, st(stream));
+}
+
 int vila_hgrn2_scan(const vila_hgrn2_params* p, void* stream) {
   VB_REQUIRE_DEVICE();
   return vb::hgrn2_scan(*p, st(stream));

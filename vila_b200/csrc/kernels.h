@@ -240,7 +240,10 @@ int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int 
 struct vila_glinear_params;
 struct vila_latent_attn_params;
 struct vila_hgrn2_params;
+struct vila_sink_attn_params;
 namespace vb {
+int sink_attention(const vila_sink_attn_params& p, cudaStream_t stream);
+int gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes, cudaStream_t stream);
 int glinear(const vila_glinear_params& p, cudaStream_t stream);
 int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream);
 int hgrn2_scan(const vila_hgrn2_params& p, cudaStream_t stream);

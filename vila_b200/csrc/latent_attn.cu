@@ -31,9 +31,13 @@ __host__ __device__ __forceinline__ int round4(int r) { return (r + 3) & ~3; }
 
 // One warp per latent row: the page-table lookup happens once per row, the row is read with 16-byte
 // loads when its width allows and widened to fp32.  Rows past nkeys and the pad columns are zero.
-__device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, const void* cache, int dt,
-                                                  const int32_t* pt, int page, int j0, int nkeys, int R) {
+// Source row of key j: through a page table (pt != nullptr: pool row, elements row * ld + col0) or
+// contiguous from first_row.
+__device__ __forceinline__ void load_rows_block(float* Cs, int RS, int R4, const void* src, int dt,
+                                                const int32_t* pt, int page, size_t first_row, int64_t ld,
+                                                size_t col0, int j0, int nkeys, int R) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool al8 = (R & 7) == 0 && (ld & 7) == 0 && (col0 & 7) == 0;
   for (int jj = warp; jj < BKEY; jj += nw) {
     float* dst = Cs + jj * RS;
     const int j = j0 + jj;
@@ -41,11 +45,12 @@ __device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, con
       for (int k = lane; k < R4; k += 32) dst[k] = 0.f;
       continue;
     }
-    const size_t row = cache_row(pt, page, j);
-    if (dt == VILA_DT_BF16 && (R & 7) == 0) {
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(cache) + row * R);
+    const size_t row = pt ? cache_row(pt, page, j) : first_row + j;
+    const size_t off = row * ld + col0;
+    if (dt == VILA_DT_BF16 && al8) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(src) + off);
       for (int v = lane; v < (R >> 3); v += 32) {
-        const uint4 u = __ldg(src + v);
+        const uint4 u = __ldg(s4 + v);
         float4 a, b;
         a.x = __uint_as_float(u.x << 16); a.y = __uint_as_float(u.x & 0xffff0000u);
         a.z = __uint_as_float(u.y << 16); a.w = __uint_as_float(u.y & 0xffff0000u);
@@ -54,13 +59,20 @@ __device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, con
         *reinterpret_cast<float4*>(dst + 8 * v) = a;
         *reinterpret_cast<float4*>(dst + 8 * v + 4) = b;
       }
-    } else if (dt == VILA_DT_F32 && (R & 3) == 0) {
-      const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(cache) + row * R);
-      for (int v = lane; v < (R >> 2); v += 32) *reinterpret_cast<float4*>(dst + 4 * v) = __ldg(src + v);
+    } else if (dt == VILA_DT_F32 && al8) {
+      const float4* s4 = reinterpret_cast<const float4*>(static_cast<const float*>(src) + off);
+      for (int v = lane; v < (R >> 2); v += 32) *reinterpret_cast<float4*>(dst + 4 * v) = __ldg(s4 + v);
     } else {
-      for (int k = lane; k < R4; k += 32) dst[k] = k < R ? ld_any(cache, dt, row * R + k) : 0.f;
+      for (int k = lane; k < R4; k += 32) dst[k] = k < R ? ld_any(src, dt, off + k) : 0.f;
     }
   }
+}
+
+// One warp per latent row: the page-table lookup happens once per row, the row is read with 16-byte
+// loads when its width allows and widened to fp32.  Rows past nkeys and the pad columns are zero.
+__device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, const void* cache, int dt,
+                                                  const int32_t* pt, int page, int j0, int nkeys, int R) {
+  load_rows_block(Cs, RS, R4, cache, dt, pt, page, 0, R, 0, j0, nkeys, R);
 }
 
 // thread (i = tid / 16, l = tid % 16): scores of query i for keys l and l + 16 of the block (float4
@@ -249,6 +261,120 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   }
 }
 
+
+// Separate keys and values (the un-folded form, for prompt portions that are a large part of their
+// context): same thread layout and online softmax as latent_attn_tile_kernel, K rows of width dim for
+// the scores, V rows of width vdim for the weighted sum, both contiguous per sequence.
+template <int KK4>
+__global__ void __launch_bounds__(kThreads) sink_attn_tile_kernel(const vila_sink_attn_params p) {
+  extern __shared__ __align__(16) float sm[];
+  const int D = p.dim, D4 = round4(D), DS = D4 + 4, V = p.vdim, V4 = round4(V), VS = V4 + 4;
+  float* Qs = sm;                  // [BQ][D4]
+  float* Ks = Qs + BQ * D4;        // [BKEY][DS]
+  float* Vs = Ks + BKEY * DS;      // [BKEY][VS]
+  float* Ps = Vs + BKEY * VS;      // [BQ][BKEY]
+  const int tid = threadIdx.x, i = tid >> 4, l = tid & 15;
+  const int h = blockIdx.y;
+  const int* tile = p.tiles + 4 * blockIdx.x;
+  const int row0 = tile[0], n = tile[1], pos0 = tile[2];
+  const size_t kv0 = static_cast<size_t>(tile[3]);
+  for (int idx = tid; idx < BQ * D4; idx += kThreads) {
+    const int qi = idx / D4, k = idx % D4;
+    Qs[idx] = (qi < n && k < D)
+                  ? ld_any(p.q, p.q_dtype, static_cast<size_t>(row0 + qi) * p.ldq + static_cast<size_t>(h) * D + k) * p.scale
+                  : 0.f;
+  }
+  float m = p.sink ? p.sink[h] : kNegBig;
+  float lsum = p.sink ? 1.0f : 0.0f;
+  float4 acc[KK4];
+#pragma unroll
+  for (int kk = 0; kk < KK4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int nkeys = pos0 + n;
+  const int my_last = pos0 + i;
+  for (int j0 = 0; j0 < nkeys; j0 += BKEY) {
+    __syncthreads();
+    load_rows_block(Ks, DS, D4, p.k, p.kv_dtype, nullptr, 1, kv0, p.ldk, static_cast<size_t>(h) * D, j0, nkeys, D);
+    load_rows_block(Vs, VS, V4, p.v, p.kv_dtype, nullptr, 1, kv0, p.ldv, static_cast<size_t>(h) * V, j0, nkeys, V);
+    __syncthreads();
+    float s0 = 0.f, s1 = 0.f;
+    const float4* qr = reinterpret_cast<const float4*>(Qs + i * D4);
+    const float4* c0 = reinterpret_cast<const float4*>(Ks + l * DS);
+    const float4* c1 = reinterpret_cast<const float4*>(Ks + (l + 16) * DS);
+#pragma unroll 4
+    for (int k = 0; k < (D4 >> 2); ++k) {
+      const float4 qv = qr[k], a = c0[k], b = c1[k];
+      s0 = fmaf(qv.x, a.x, s0); s0 = fmaf(qv.y, a.y, s0); s0 = fmaf(qv.z, a.z, s0); s0 = fmaf(qv.w, a.w, s0);
+      s1 = fmaf(qv.x, b.x, s1); s1 = fmaf(qv.y, b.y, s1); s1 = fmaf(qv.z, b.z, s1); s1 = fmaf(qv.w, b.w, s1);
+    }
+    const bool v0 = i < n && j0 + l <= my_last, v1 = i < n && j0 + l + 16 <= my_last;
+    s0 = v0 ? s0 : kNegBig;
+    s1 = v1 ? s1 : kNegBig;
+    float bm = fmaxf(s0, s1);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, o));
+    const float m_new = fmaxf(m, bm);
+    const float alpha = expf(m - m_new);
+    const float p0 = v0 ? expf(s0 - m_new) : 0.f, p1 = v1 ? expf(s1 - m_new) : 0.f;
+    float ps = p0 + p1;
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+    lsum = lsum * alpha + ps;
+    m = m_new;
+    Ps[i * BKEY + l] = p0;
+    Ps[i * BKEY + l + 16] = p1;
+    __syncthreads();
+    const float* pr = Ps + i * BKEY;
+#pragma unroll
+    for (int kk = 0; kk < KK4; ++kk) {
+      acc[kk].x *= alpha; acc[kk].y *= alpha; acc[kk].z *= alpha; acc[kk].w *= alpha;
+    }
+#pragma unroll 4
+    for (int jj = 0; jj < BKEY; ++jj) {
+      const float pj = pr[jj];
+      const float* cr = Vs + jj * VS + 4 * l;
+#pragma unroll
+      for (int kk = 0; kk < KK4; ++kk) {
+        if (4 * l + 64 * kk < V4) {
+          const float4 c = *reinterpret_cast<const float4*>(cr + 64 * kk);
+          acc[kk].x = fmaf(pj, c.x, acc[kk].x); acc[kk].y = fmaf(pj, c.y, acc[kk].y);
+          acc[kk].z = fmaf(pj, c.z, acc[kk].z); acc[kk].w = fmaf(pj, c.w, acc[kk].w);
+        }
+      }
+    }
+  }
+  if (i < n) {
+    const size_t row = row0 + i;
+    float g = 1.0f / lsum;
+    if (p.gate) g *= sigmoid_f(ld_any(p.gate, p.gate_dtype, row * p.ldg + h));
+    const size_t ob = row * p.ldo + static_cast<size_t>(h) * V;
+#pragma unroll
+    for (int kk = 0; kk < KK4; ++kk) {
+      const int k = 4 * l + 64 * kk;
+      const float v[4] = {acc[kk].x, acc[kk].y, acc[kk].z, acc[kk].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (k + e < V) st_any(p.out, p.out_dtype, ob + k + e, v[e] * g);
+    }
+  }
+}
+
+// dst[i] = src[rows[i]]: one warp per row, 16-byte pieces when everything is 16-byte aligned
+__global__ void __launch_bounds__(kThreads) gather_rows_kernel(const unsigned char* __restrict__ src,
+                                                               const int32_t* __restrict__ rows,
+                                                               unsigned char* __restrict__ dst, int n_rows,
+                                                               int row_bytes, int vec) {
+  const int r = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= n_rows) return;
+  const unsigned char* s = src + static_cast<size_t>(rows[r]) * row_bytes;
+  unsigned char* d = dst + static_cast<size_t>(r) * row_bytes;
+  if (vec) {
+    for (int b = lane; b < (row_bytes >> 4); b += 32)
+      reinterpret_cast<uint4*>(d)[b] = __ldg(reinterpret_cast<const uint4*>(s) + b);
+  } else {
+    for (int b = lane; b < row_bytes; b += 32) d[b] = s[b];
+  }
+}
+
 template <typename K>
 int set_smem(K kern, size_t bytes) {
   if (bytes > 48 * 1024)
@@ -289,6 +415,37 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   else if (p.R <= 256) VB_LAT_TILE(4);
   else VB_LAT_TILE(8);
 #undef VB_LAT_TILE
+  return 0;
+}
+
+int sink_attention(const vila_sink_attn_params& p, cudaStream_t stream) {
+  if (p.ntiles <= 0) return 0;
+  VB_CHECK(p.dim >= 1 && p.dim <= 512 && p.vdim >= 1 && p.vdim <= 512 && p.H >= 1 && p.H <= 65535,
+           "sink_attention: H=%d dim=%d vdim=%d (dims <= 512)", p.H, p.dim, p.vdim);
+  const int d4 = round4(p.dim), v4 = round4(p.vdim);
+  const size_t smem = sizeof(float) * (BQ * d4 + BKEY * (d4 + 4) + BKEY * (v4 + 4) + BQ * BKEY);
+  const dim3 grid(p.ntiles, p.H), block(kThreads);
+#define VB_SINK_TILE(KK)                                                                 \
+  do {                                                                                   \
+    if (set_smem(sink_attn_tile_kernel<KK>, smem)) return 2;                             \
+    VB_CUDA(launch_serial(sink_attn_tile_kernel<KK>, grid, block, smem, stream, p));     \
+  } while (0)
+  if (p.vdim <= 64) VB_SINK_TILE(1);
+  else if (p.vdim <= 128) VB_SINK_TILE(2);
+  else if (p.vdim <= 256) VB_SINK_TILE(4);
+  else VB_SINK_TILE(8);
+#undef VB_SINK_TILE
+  return 0;
+}
+
+int gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  VB_CHECK(row_bytes > 0, "gather_rows: row_bytes=%d", row_bytes);
+  const int vec = row_bytes % 16 == 0 && reinterpret_cast<uintptr_t>(src) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(dst) % 16 == 0;
+  VB_CUDA(launch_serial(gather_rows_kernel, dim3((n_rows + 7) / 8), dim3(kThreads), 0, stream,
+                        static_cast<const unsigned char*>(src), rows, static_cast<unsigned char*>(dst), n_rows,
+                        row_bytes, vec));
   return 0;
 }
 

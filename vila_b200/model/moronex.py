@@ -266,6 +266,7 @@ class MoronexForCausalLM:
                 # key expansion per head, transposed: q'_h = uk_t[h] q_h, uk_t [H, R, dim]
                 L.uk_t = w(p + "mix.uk").view(lc.heads, lc.dim, lc.kv_rank).transpose(1, 2).contiguous()
                 L.uv = w(p + "mix.uv").view(lc.heads, lc.vdim, lc.kv_rank).contiguous()
+                L.ukv, L.ukv_off = cat_rows([p + "mix.uk", p + "mix.uv"])   # un-folded form: one expansion GEMM
                 L.sink = f32(p + "mix.sink")
                 L.latent_layer = i if lc.kv_from is None else lc.kv_from
             else:
@@ -327,17 +328,30 @@ class MoronexForCausalLM:
             a, n = L.in_off[f"l{L.index}.mix.dkv"]
             ops.rmsnorm_rows(P[:, a:a + n], L.dkv_norm, eps, out=pool, out_rows=batch.cache_rows)
         q = self._lin(cq, L.uq)
-        R = lc.kv_rank
-        qa = ops.glinear(q, L.uk_t, groups=lc.heads, a_group_off=lc.dim, o_group_off=R, out_dtype=torch.float32)
+        R, T = lc.kv_rank, h.shape[0]
         a, _ = L.in_off[f"l{L.index}.mix.g"]
         gate = P[:, a:a + lc.heads]
-        ol = torch.empty(qa.shape, dtype=self.dtype, device=self.device)
-        kw = dict(heads=lc.heads, page=cache.page, scale=lc.scale, sink=L.sink, gate=gate, out=ol)
-        if batch.tiles is not None:
-            ops.latent_attention(qa, pool, cache.page_tables, batch.tiles, **kw)
-        if batch.decode_tiles is not None:
-            ops.latent_attention(qa, pool, cache.page_tables, batch.decode_tiles, decode=True, **kw)
-        o = ops.glinear(ol, L.uv, groups=lc.heads, a_group_off=R, o_group_off=lc.vdim)
+        o = None
+        if batch.tiles is not None or batch.decode_tiles is not None:
+            # folded form: attend over the cached latents themselves
+            qa = ops.glinear(q, L.uk_t, groups=lc.heads, a_group_off=lc.dim, o_group_off=R, out_dtype=torch.float32)
+            alloc = torch.zeros if batch.kv_tiles is not None else torch.empty   # rows of the other form stay finite
+            ol = alloc(qa.shape, dtype=self.dtype, device=self.device)
+            kw = dict(heads=lc.heads, page=cache.page, scale=lc.scale, sink=L.sink, gate=gate, out=ol)
+            if batch.tiles is not None:
+                ops.latent_attention(qa, pool, cache.page_tables, batch.tiles, **kw)
+            if batch.decode_tiles is not None:
+                ops.latent_attention(qa, pool, cache.page_tables, batch.decode_tiles, decode=True, **kw)
+            o = ops.glinear(ol, L.uv, groups=lc.heads, a_group_off=R, o_group_off=lc.vdim)
+        if batch.kv_tiles is not None:
+            # un-folded form: expand keys and values of the whole context of these sequences once
+            kv = self._lin(ops.gather_rows(pool, batch.ctx_rows), L.ukv)
+            ka, kn = L.ukv_off[f"l{L.index}.mix.uk"]
+            va, vn = L.ukv_off[f"l{L.index}.mix.uv"]
+            if o is None:
+                o = torch.empty(T, lc.heads * lc.vdim, dtype=self.dtype, device=self.device)
+            ops.sink_attention(q, kv[:, ka:ka + kn], kv[:, va:va + vn], batch.kv_tiles, heads=lc.heads,
+                               scale=lc.scale, sink=L.sink, gate=gate, out=o)
         a, n = L.in_off[f"l{L.index}.rg1"]
         return self._lin(o, L.o), P[:, a:a + n]
 

@@ -570,3 +570,37 @@ def moe_group(idx: torch.Tensor, experts: int):
     check(_lib.load().vila_moe_group(_i32(idx, "idx"), _p(seg), _p(srt), pairs, experts, _stream()),
           "vila_moe_group")
     return seg, srt[:pairs]
+
+
+def gather_rows(src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    """src [N, C] contiguous, rows int32 [n] -> src[rows] (any dtype)."""
+    assert src.dim() == 2 and src.is_contiguous() and src.is_cuda
+    out = torch.empty(rows.numel(), src.shape[1], dtype=src.dtype, device=src.device)
+    check(_lib.load().vila_gather_rows(_p(src), _i32(rows, "rows"), _p(out), rows.numel(),
+                                       src.shape[1] * src.element_size(), _stream()), "vila_gather_rows")
+    return out
+
+
+def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tiles: torch.Tensor, *, heads: int,
+                   scale: float, sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None, out_dtype=None) -> torch.Tensor:
+    """Causal attention with separate keys / values, fp32 softmax, optional sink and output gate.
+    q [T, heads * dim]; k [rows, heads * dim], v [rows, heads * vdim] (views with a row stride are fine):
+    every sequence's positions 0.. contiguous from its kv_row0; tiles int32 [n, 4] = (row0, rows, pos0,
+    kv_row0) -> [T, heads * vdim]."""
+    assert q.dim() == 2 and k.dim() == 2 and v.dim() == 2 and q.stride(1) == k.stride(1) == v.stride(1) == 1
+    assert k.dtype == v.dtype and q.shape[1] == k.shape[1] and k.shape[1] % heads == 0 and v.shape[1] % heads == 0
+    dim, vdim = k.shape[1] // heads, v.shape[1] // heads
+    if out is None:
+        out = torch.empty(q.shape[0], heads * vdim, dtype=out_dtype or q.dtype, device=q.device)
+    assert out.shape == (q.shape[0], heads * vdim) and out.stride(1) == 1
+    p = _lib.SinkAttnParams()
+    p.q, p.k, p.v, p.out = _p(q), _p(k), _p(v), _p(out)
+    p.tiles, p.sink, p.gate = _i32(tiles, "tiles"), _f32(sink, "sink"), _p(gate)
+    p.ldq, p.ldk, p.ldv, p.ldo = q.stride(0), k.stride(0), v.stride(0), out.stride(0)
+    p.ldg = gate.stride(0) if gate is not None else 0
+    p.q_dtype, p.kv_dtype, p.out_dtype = _dt(q, "q"), _dt(k, "k"), _dt(out, "out")
+    p.gate_dtype = _dt(gate, "gate") if gate is not None else 0
+    p.ntiles, p.H, p.dim, p.vdim, p.scale = tiles.shape[0], heads, dim, vdim, scale
+    check(_lib.load().vila_sink_attention(C.byref(p), _stream()), "vila_sink_attention")
+    return out

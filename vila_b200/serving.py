@@ -261,9 +261,14 @@ class RaggedBatch:
     tiles = the multi-row sequences cut into <= 16-row pieces, decode_tiles = the single-row ones
     (same 4 columns); cache_rows[t] = pool row of token t in the paged caches."""
 
-    def __init__(self, ids, cache_rows, seqs, tiles, decode_tiles):
+
+    def __init__(self, ids, cache_rows, seqs, tiles, decode_tiles, ctx_rows=None, kv_tiles=None):
         self.ids, self.cache_rows, self.seqs = ids, cache_rows, seqs
         self.tiles, self.decode_tiles = tiles, decode_tiles
+        # un-folded attention for prompt portions that are a large part of their context: ctx_rows = pool
+        # rows of ALL positions of those sequences, kv_tiles = their tiles as (row0, rows, pos0, first row
+        # of the sequence inside ctx_rows); `tiles` is None then
+        self.ctx_rows, self.kv_tiles = ctx_rows, kv_tiles
         self.T = ids.numel()
 
 
@@ -305,6 +310,9 @@ class TokenEngine:
         # steps made of single decoded tokens only: one CUDA graph per row count (index arrays live in
         # static buffers, page tables and state pools are static already); a row count is run eagerly
         # the first time it occurs, captured the second time, replayed from then on
+        # prompt portions whose rows x unfold_ratio reach the context they attend to are served by expanding
+        # keys / values once per step (4x fewer attention flops at kv_rank = 4 x head size); 0: never
+        self.unfold_ratio = 4
         self.graphs = graphs
         self._decode_graphs: Dict[int, tuple] = {}
         self._decode_seen: Dict[int, int] = {}
@@ -342,6 +350,7 @@ class TokenEngine:
     def _build(self, entries):
         c, dev = self.cache, self.model.device
         ids, rows, seqs, tiles, dec, want_rows = [], [], [], [], [], []
+        ctx, kv_tiles, ctx_at = [], [], 0
         dirty, at = False, 0
         for seq_id, tokens, want in entries:
             n = len(tokens)
@@ -359,14 +368,25 @@ class TokenEngine:
             else:
                 for o in range(0, n, TILE_ROWS):
                     tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, s.slot))
+                    kv_tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, ctx_at))
+                allpos = np.arange(0, s.length + n)
+                ctx.append(pages[allpos // c.page] * c.page + allpos % c.page)
+                ctx_at += s.length + n
             want_rows.extend(at + int(k) for k in want)
             s.length += n
             at += n
         if dirty:
             c.page_tables.copy_(torch.from_numpy(c.page_tables_host))
+        tile_rows = sum(t[1] for t in tiles)
+        unfold = bool(tiles) and self.unfold_ratio > 0 and tile_rows * self.unfold_ratio >= ctx_at
+        if unfold:
+            tiles = []
+        else:
+            ctx, kv_tiles = [], []
         # one host->device copy for all index arrays of the step
         parts = [np.concatenate(ids), np.concatenate(rows), np.asarray(seqs).reshape(-1),
-                 np.asarray(tiles).reshape(-1), np.asarray(dec).reshape(-1)]
+                 np.asarray(tiles).reshape(-1), np.asarray(dec).reshape(-1),
+                 np.concatenate(ctx) if ctx else np.zeros(0), np.asarray(kv_tiles).reshape(-1)]
         flat = torch.from_numpy(np.concatenate(parts).astype(np.int32))
         return flat, [p.size for p in parts], want_rows
 
@@ -375,7 +395,8 @@ class TokenEngine:
         cuts = np.cumsum([0] + list(sizes))
         v = [flat[cuts[i]:cuts[i + 1]] for i in range(len(sizes))]
         return RaggedBatch(v[0], v[1], v[2].view(-1, 4), v[3].view(-1, 4) if sizes[3] else None,
-                           v[4].view(-1, 4) if sizes[4] else None)
+                           v[4].view(-1, 4) if sizes[4] else None, v[5] if sizes[5] else None,
+                           v[6].view(-1, 4) if sizes[6] else None)
 
     def _decode_step_graphed(self, flat, sizes) -> Tuple[torch.Tensor, torch.Tensor]:
         """All rows are single decoded tokens: replay (or capture) the graph of this row count.
@@ -407,7 +428,7 @@ class TokenEngine:
             return None
         flat, sizes, want_rows = self._build(entries)
         T = sizes[0]
-        decode_only = sizes[3] == 0 and layer_outputs is None
+        decode_only = sizes[3] == 0 and sizes[6] == 0 and layer_outputs is None
         if self.graphs and decode_only and self._decode_seen.get(T, 0) >= 1:
             x, all_logits = self._decode_step_graphed(flat, sizes)
             if not want_rows:
