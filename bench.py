@@ -1066,7 +1066,13 @@ def hybrid_lm_block(args, peaks):
         tiles = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
         t = timed(lambda: ops.latent_attention(qa, pool, pt, tiles, heads=H, page=page, scale=0.088, sink=L0.sink, gate=gate))
         fl = H * (S * (S + 1) / 2) * 4 * R
-        led["latent_attention prefill (CUDA cores, fp32 scores and weights)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        led["latent_attention prefill, folded over the latent (CUDA cores, fp32 scores and weights)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        kvb = torch.randn(S, H * 256, device=dev).to(bf)
+        qb = torch.randn(S, H * 128, device=dev).to(bf)
+        kvt = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
+        t = timed(lambda: ops.sink_attention(qb, kvb[:, :H * 128], kvb[:, H * 128:], kvt, heads=H, scale=0.088, sink=L0.sink, gate=gate))
+        fl = H * (S * (S + 1) / 2) * 4 * 128
+        led["sink_attention prefill, un-folded keys / values (CUDA cores, fp32 scores and weights)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
         q3 = torch.randn(S, H + 8, 128, device=dev).to(bf)
         cache = qw.new_cache(S)
         t = timed(lambda: ops.fmha(q3[:, :H], cache.k(0), cache.v(0), B=1, Sq=S, Sk=S, causal=True, scale=0.088, page_table=cache.page_table))

@@ -229,10 +229,10 @@ __global__ void __launch_bounds__(kThreads) glinear_wmma_kernel(const vila_gline
 
 // ---- few rows per group (decoded tokens): weight-streaming kernel ---------------------------------
 // One warp per PAIR of output columns; the lanes split K in 8-element pieces (16-byte loads of bf16
-// weights, 32-byte of fp32), every weight byte is read once per chunk of up to 16 rows, the rows of A
-// come from L1 / L2.  Serves the routed experts, the per-head folded projections and the output head
+// weights, 32-byte of fp32), every weight byte is read once per pass, the rows of A
+// come from L1 / L2 (a pass covers up to 8 rows; more rows of a group mean more passes).  Serves the routed experts, the per-head folded projections and the output head
 // of decode steps, all of which are bound by the weight stream.
-constexpr int kSmallRows = 16, kSmallWarps = 8;
+constexpr int kSmallRows = 8, kSmallWarps = 8;   // rows per pass over the weights
 
 __device__ __forceinline__ void load8(const void* p, int dt, size_t i, float (&v)[8]) {
   if (dt) {
@@ -285,6 +285,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
     for (int r = 0; r < kSmallRows; ++r) acc_a[r] = acc_b[r] = 0.f;
     if (has_a) {
       if (vec) {
+#pragma unroll 2
         for (int k = lane * 8; k < p.K; k += 256) {
           float w0[8], w1[8], a[8];
           load8(p.w, p.w_dtype, wa + k, w0);
@@ -351,7 +352,7 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
   VB_CHECK(p.a_rows == nullptr || p.a_row_div >= 1, "glinear: a_row_div=%d", p.a_row_div);
   const bool small = p.M <= 16;
   // few rows: stream the weights once per 16-row chunk instead of tiling
-  if ((p.mode == 0 && p.M <= kSmallRows) || (p.mode == 1 && p.M <= 4 * kSmallRows)) {
+  if ((p.mode == 0 && p.M <= 2 * kSmallRows) || (p.mode == 1 && p.M <= 8 * kSmallRows)) {
     const size_t ea = p.a_dtype ? 4 : 2, ew = p.w_dtype ? 4 : 2;
     const bool vec = p.K % 8 == 0 && p.lda % 8 == 0 && p.ldw % 8 == 0 && p.w_group_stride % 8 == 0 &&
                      p.a_group_off % 8 == 0 && reinterpret_cast<uintptr_t>(p.a) % (8 * ea) == 0 &&
