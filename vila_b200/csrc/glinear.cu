@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
 }
 
 // ---- bf16 operands, many rows: warp-level tensor-core tiles (wmma, fp32 accumulators) ---------------
-// Same tiling contract as glinear_kernel<64> (64 x 64 outputs per CTA, groups, row gather / scatter,
+// Same tiling as glinear_kernel<64> (64 x 64 outputs per CTA, groups, row gather / scatter,
 // epilogues); 8 warps as 4 x 2, each 16 x 32 outputs; K in steps of 32 through shared memory.  The
 // accumulators go through shared memory once so that the epilogue is the shared one.
 constexpr int WK = 32, WLD = WK + 8;
