@@ -1080,7 +1080,7 @@ def hybrid_lm_block(args, peaks):
         led["qwen2 fmha prefill (tcgen05)"] = {"ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
         dt_ = torch.tensor([(b, 1, CTX - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
         pt2 = (torch.arange(B, device=dev, dtype=torch.int32)[:, None] * (CTX // page) + torch.arange(eng.cache.n_pages, device=dev, dtype=torch.int32)[None]) % eng.cache.n_pages
-        t = timed(lambda: ops.latent_attention(qa[:B], pool, pt2.contiguous(), dt_, heads=H, page=page, scale=0.088, sink=L0.sink, gate=gate[:B], decode=True))
+        t = timed(lambda: ops.latent_attention(qa[:B], pool, pt2.contiguous(), dt_, heads=H, page=page, scale=0.088, sink=L0.sink, gate=gate[:B], decode=True, nsplit=eng.cache.decode_splits))
         by = B * CTX * R * 2
         led["latent_attention decode (8 x 1024 tokens)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs,
                                                             "note": "unique latent bytes; each of the H head CTAs re-reads them through L2"}

@@ -364,7 +364,9 @@ int vila_glinear(const vila_glinear_params* p, void* stream);
  * sink == NULL: ordinary softmax; gate == NULL: no output gate.  The latent lives in pages of
  * `page` tokens: token j of a sequence is row page_tables[slot * pt_stride + j / page] * page + j % page.
  * tiles [ntiles, 4] = (first batch row, rows (<= 16), position of the first row, slot): consecutive
- * rows of one sequence.  decode != 0 selects the one-row-per-tile kernel (all rows must be 1). */
+ * rows of one sequence.  decode != 0 selects the one-row-per-tile kernel (all rows must be 1); with
+ * nsplit > 1 the 32-key blocks of a row are dealt round-robin to nsplit CTAs whose partial results
+ * (partial: fp32 [T, H, nsplit, R + 2], caller-owned) are merged by a second kernel. */
 typedef struct vila_latent_attn_params {
   const float* q; /* [T, H, R] */
   const void* cache;
@@ -373,9 +375,10 @@ typedef struct vila_latent_attn_params {
   const float* sink;
   const void* gate;
   void* out; /* [T, H, R] */
+  float* partial;
   int64_t ldg;
   int32_t cache_dtype, gate_dtype, out_dtype;
-  int32_t ntiles, pt_stride, H, R, page, decode;
+  int32_t ntiles, pt_stride, H, R, page, decode, nsplit;
   float scale;
 } vila_latent_attn_params;
 int vila_latent_attention(const vila_latent_attn_params* p, void* stream);

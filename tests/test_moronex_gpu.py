@@ -300,6 +300,9 @@ def test_latent_attention_kernels(cuda, dtype, R, H):
     sg = torch.tensor(single, dtype=torch.int32).cuda()
     got1 = ops.latent_attention(q.view(T, -1).cuda(), pool, pt.cuda(), sg, decode=True, **common)
     assert rel(got1.view(T, H, R), want) < t
+    for ns in (2, 5, 16):   # keys of a row dealt to several CTAs and merged (more CTAs than key blocks too)
+        gots = ops.latent_attention(q.view(T, -1).cuda(), pool, pt.cuda(), sg, decode=True, nsplit=ns, **common)
+        assert rel(gots.view(T, H, R), want) < t, ns
     # no sink, no gate
     plain = ops.latent_attention(q.view(T, -1).cuda(), pool, pt.cuda(), tl, heads=H, page=page, scale=0.2, out_dtype=F32)
     at, w2 = 0, []
@@ -326,7 +329,7 @@ def test_latent_attention_far_key_and_sink_show(cuda, decode):
         pool[int(pt[0, j // page]) * page + j % page] = c[j]
     q = (c[far] * 4)[None, None].repeat(1, H, 1).reshape(1, -1)
     tile = torch.tensor([[0, 1, L - 1, 0]], dtype=torch.int32).cuda()
-    kw = dict(heads=H, page=page, scale=1.0, out_dtype=F32, decode=decode)
+    kw = dict(heads=H, page=page, scale=1.0, out_dtype=F32, decode=decode, nsplit=4 if decode else 1)
     out = ops.latent_attention(q.cuda(), pool.cuda(), pt.cuda(), tile, **kw).view(H, R)
     assert rel(out[0], c[far]) < 1e-4 and rel(out[1], c[far]) < 1e-4
     # one position earlier than the key's own: invisible

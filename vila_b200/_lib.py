@@ -85,10 +85,10 @@ class GLinearParams(C.Structure):
 class LatentAttnParams(C.Structure):
     _fields_ = [
         ("q", c_void_p), ("cache", c_void_p), ("page_tables", c_void_p), ("tiles", c_void_p),
-        ("sink", c_void_p), ("gate", c_void_p), ("out", c_void_p), ("ldg", c_i64),
+        ("sink", c_void_p), ("gate", c_void_p), ("out", c_void_p), ("partial", c_void_p), ("ldg", c_i64),
         ("cache_dtype", C.c_int32), ("gate_dtype", C.c_int32), ("out_dtype", C.c_int32),
         ("ntiles", C.c_int32), ("pt_stride", C.c_int32), ("H", C.c_int32), ("R", C.c_int32),
-        ("page", C.c_int32), ("decode", C.c_int32), ("scale", c_float),
+        ("page", C.c_int32), ("decode", C.c_int32), ("nsplit", C.c_int32), ("scale", c_float),
     ]
 
 

@@ -176,7 +176,7 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   const int R = p.R, R4 = round4(R), RS = R4 + 4;
   float* Qs = sm;               // [R4]
   float* Cs = Qs + R4;          // [BKEY][RS]
-  float* Ps = Cs + BKEY * RS;   // [BKEY] + alpha + sum
+  float* Ps = Cs + BKEY * RS;   // [BKEY] + alpha + sum + max
   const int tid = threadIdx.x;
   const int h = blockIdx.y;
   const int* tile = p.tiles + 4 * blockIdx.x;
@@ -192,11 +192,14 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   float acc[KK];
 #pragma unroll
   for (int kk = 0; kk < KK; ++kk) acc[kk] = 0.f;
-  float m = p.sink ? p.sink[h] : kNegBig;   // meaningful in warp 0 only
-  float lsum = p.sink ? 1.0f : 0.0f;
+  // split s of nsplit takes the key blocks s, s + nsplit, ...; the sink belongs to split 0
+  const int split = blockIdx.z, nsplit = p.nsplit;
+  const bool has_sink = p.sink != nullptr && split == 0;
+  float m = has_sink ? p.sink[h] : kNegBig;   // meaningful in warp 0 only
+  float lsum = has_sink ? 1.0f : 0.0f;
   const int nkeys = pos0 + 1;
   const int jj_s = tid >> 3, sub = tid & 7;
-  for (int j0 = 0; j0 < nkeys; j0 += BKEY) {
+  for (int j0 = split * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
     __syncthreads();
     load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
@@ -236,7 +239,10 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
     }
   }
   __syncthreads();
-  if (tid == 0) Ps[BKEY + 1] = lsum;
+  if (tid == 0) {
+    Ps[BKEY + 1] = lsum;
+    Ps[BKEY + 2] = m;
+  }
   // cross-group reduction through Cs (reused): [G][R]
   if (G > 1) {
     if (kcol < R) Cs[jg * R + kcol] = acc[0];
@@ -248,6 +254,22 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
     }
   } else {
     __syncthreads();
+  }
+  if (nsplit > 1) {
+    // un-normalised partial result of this split: R sums, then the running max and sum
+    float* part = p.partial + ((static_cast<size_t>(row0) * p.H + h) * nsplit + split) * (R + 2);
+    if (jg == 0) {
+#pragma unroll
+      for (int kk = 0; kk < KK; ++kk) {
+        const int k = kcol + kThreads * kk;
+        if (k < R && (RP >= kThreads || kcol < R)) part[k] = acc[kk];
+      }
+    }
+    if (tid == 0) {
+      part[R] = Ps[BKEY + 2];
+      part[R + 1] = Ps[BKEY + 1];
+    }
+    return;
   }
   if (jg == 0) {
     float g = 1.0f / Ps[BKEY + 1];
@@ -261,6 +283,23 @@ __global__ void __launch_bounds__(kThreads) latent_attn_decode_kernel(const vila
   }
 }
 
+// Merge of the nsplit partial results of a (row, head): weights exp(m_s - max m), fixed order.
+__global__ void __launch_bounds__(kThreads) latent_attn_merge_kernel(const vila_latent_attn_params p) {
+  const int h = blockIdx.y, R = p.R, ns = p.nsplit;
+  const int row0 = p.tiles[4 * blockIdx.x];
+  const float* part = p.partial + (static_cast<size_t>(row0) * p.H + h) * ns * (R + 2);
+  float mx = kNegBig;
+  for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part[s * (R + 2) + R]);
+  float den = 0.f;
+  for (int s = 0; s < ns; ++s) den += expf(part[s * (R + 2) + R] - mx) * part[s * (R + 2) + R + 1];
+  float g = 1.0f / den;
+  if (p.gate) g *= sigmoid_f(ld_any(p.gate, p.gate_dtype, static_cast<size_t>(row0) * p.ldg + h));
+  for (int k = threadIdx.x; k < R; k += kThreads) {
+    float a = 0.f;
+    for (int s = 0; s < ns; ++s) a += expf(part[s * (R + 2) + R] - mx) * part[s * (R + 2) + k];
+    st_any(p.out, p.out_dtype, (static_cast<size_t>(row0) * p.H + h) * R + k, a * g);
+  }
+}
 
 // Separate keys and values (the un-folded form, for prompt portions that are a large part of their
 // context): same thread layout and online softmax as latent_attn_tile_kernel, K rows of width dim for
@@ -393,14 +432,18 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
     int rp = 1;
     while (rp < p.R) rp <<= 1;
     const int r4 = round4(p.R);
-    const size_t smem = sizeof(float) * (r4 + BKEY * (r4 + 4) + BKEY + 2);
+    const size_t smem = sizeof(float) * (r4 + BKEY * (r4 + 4) + BKEY + 4);
+    VB_CHECK(p.nsplit >= 1 && p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
+             "latent_attention: nsplit=%d needs 1..64 and a partial buffer", p.nsplit);
+    const dim3 dgrid(p.ntiles, p.H, p.nsplit);
     if (p.R <= 256) {
       if (set_smem(latent_attn_decode_kernel<1>, smem)) return 2;
-      VB_CUDA(launch_serial(latent_attn_decode_kernel<1>, grid, block, smem, stream, p, rp));
+      VB_CUDA(launch_serial(latent_attn_decode_kernel<1>, dgrid, block, smem, stream, p, rp));
     } else {
       if (set_smem(latent_attn_decode_kernel<2>, smem)) return 2;
-      VB_CUDA(launch_serial(latent_attn_decode_kernel<2>, grid, block, smem, stream, p, rp));
+      VB_CUDA(launch_serial(latent_attn_decode_kernel<2>, dgrid, block, smem, stream, p, rp));
     }
+    if (p.nsplit > 1) VB_CUDA(launch_serial(latent_attn_merge_kernel, grid, block, 0, stream, p));
     return 0;
   }
   const int r4 = round4(p.R);

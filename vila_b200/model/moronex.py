@@ -341,7 +341,8 @@ class MoronexForCausalLM:
             if batch.tiles is not None:
                 ops.latent_attention(qa, pool, cache.page_tables, batch.tiles, **kw)
             if batch.decode_tiles is not None:
-                ops.latent_attention(qa, pool, cache.page_tables, batch.decode_tiles, decode=True, **kw)
+                ops.latent_attention(qa, pool, cache.page_tables, batch.decode_tiles, decode=True,
+                                     nsplit=cache.decode_splits, **kw)
             o = ops.glinear(ol, L.uv, groups=lc.heads, a_group_off=R, o_group_off=lc.vdim)
         if batch.kv_tiles is not None:
             # un-folded form: expand keys and values of the whole context of these sequences once

@@ -507,9 +507,10 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
 def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Tensor, tiles: torch.Tensor,
                      *, heads: int, page: int, scale: float, sink: Optional[torch.Tensor] = None,
                      gate: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, out_dtype=None,
-                     decode: bool = False) -> torch.Tensor:
+                     decode: bool = False, nsplit: int = 1) -> torch.Tensor:
     """q fp32 [T, heads * R] (key expansion already folded in), cache [pool rows, R], page_tables int32
-    [slots, max_pages], tiles int32 [ntiles, 4] (row0, rows, pos0, slot) -> [T, heads * R]."""
+    [slots, max_pages], tiles int32 [ntiles, 4] (row0, rows, pos0, slot) -> [T, heads * R].
+    decode: one-row tiles; nsplit > 1 spreads the keys of every row over nsplit CTAs + a merge kernel."""
     assert q.dtype == torch.float32 and q.is_contiguous() and q.dim() == 2
     assert cache.dim() == 2 and cache.is_contiguous()
     R = cache.shape[1]
@@ -527,6 +528,11 @@ def latent_attention(q: torch.Tensor, cache: torch.Tensor, page_tables: torch.Te
     p.gate_dtype = _dt(gate, "gate") if gate is not None else 0
     p.ntiles, p.pt_stride = tiles.shape[0], page_tables.stride(0)
     p.H, p.R, p.page, p.decode, p.scale = heads, R, page, 1 if decode else 0, scale
+    p.nsplit = max(1, int(nsplit)) if decode else 1
+    partial = None
+    if p.nsplit > 1:
+        partial = torch.empty(q.shape[0] * heads * p.nsplit * (R + 2), dtype=torch.float32, device=q.device)
+        p.partial = partial.data_ptr()
     check(_lib.load().vila_latent_attention(C.byref(p), _stream()), "vila_latent_attention")
     return out
 

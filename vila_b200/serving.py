@@ -281,6 +281,9 @@ class HybridCache:
         dev = model.device
         self.page, self.slots = page, slots
         self.n_pages = max(1, (max_tokens + page - 1) // page)
+        # decoded tokens: CTAs per (row, head) of the attention over the cache; fixed per pool so that a
+        # captured decode graph stays valid while the contexts grow (about one CTA per 256 cached tokens)
+        self.decode_splits = min(16, max(1, self.n_pages * page // 256))
         self.latent = {i: torch.zeros(self.n_pages * page, r, device=dev, dtype=model.dtype)
                        for i, r in model.latent_widths().items()}
         self.state = {i: torch.zeros(slots, *shape, device=dev, dtype=torch.float32)
