@@ -257,7 +257,7 @@ def _attend_direct(q, c, sink, gate, scale, pos0):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
-@pytest.mark.parametrize("R,H", [(20, 3), (64, 2), (130, 1), (300, 2)])
+@pytest.mark.parametrize("R,H", [(20, 3), (64, 2), (130, 1), (300, 2), (40, 6), (96, 17)])
 def test_latent_attention_kernels(cuda, dtype, R, H):
     """Portions that start and end in the middle of pages, shuffled physical pages, a second sequence in
     the same launch, with and without sink / gate; the one-row kernel at page borders."""
@@ -318,7 +318,7 @@ def test_latent_attention_far_key_and_sink_show(cuda, decode):
     the output must vanish.  Random weights would hide both among hundreds of keys."""
     ops = _ops()
     g = torch.Generator().manual_seed(7)
-    R, H, page, L = 32, 2, 64, 700
+    R, H, page, L = 32, 2, 64, 700   # (two heads: the one-head-per-CTA decode kernel; more heads: test above)
     n_pages = (L + page - 1) // page
     pt = torch.arange(n_pages - 1, -1, -1, dtype=torch.int32)[None].contiguous()   # pages in reverse order
     c = torch.randn(L, R, generator=g) * 0.1

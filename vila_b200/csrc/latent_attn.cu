@@ -6,8 +6,11 @@
 //   softmax with a sink: the running (max, sum) pair starts at (sink_h, 1) instead of (-inf, 0),
 //   which puts exp(sink_h) into the denominator exactly once, with no key and no value.
 // Scores, softmax and accumulation are fp32.  Two kernels:
-//   latent_attn_tile_kernel   up to 16 consecutive rows of one sequence per CTA (prompt portions)
-//   latent_attn_decode_kernel one row per CTA, all 256 threads spread over keys (decoded tokens)
+//   latent_attn_tile_kernel   up to 16 consecutive rows of one sequence per CTA (prompt portions), or,
+//                             for decoded tokens, up to 16 heads of one token per CTA (kHeadRows)
+//   latent_attn_decode_kernel one (token, head) per CTA, all 256 threads spread over keys (decoded
+//                             tokens of models with fewer than 4 heads)
+//   both decode forms deal the key blocks of a row to nsplit CTAs; latent_attn_merge_kernel merges them
 #include "../../include/vila_b200.h"
 #include "common.cuh"
 #include "kernels.h"
@@ -77,7 +80,7 @@ __device__ __forceinline__ void load_latent_block(float* Cs, int RS, int R4, con
 
 // thread (i = tid / 16, l = tid % 16): scores of query i for keys l and l + 16 of the block (float4
 // dot products), then the accumulator columns 4l .. 4l+3 (+ 64, + 128, ...) of query i.
-template <int KK4>
+template <int KK4, bool kHeadRows>
 __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_latent_attn_params p) {
   extern __shared__ __align__(16) float sm[];
   const int R = p.R, R4 = round4(R), RS = R4 + 4;
@@ -85,23 +88,32 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
   float* Cs = Qs + BQ * R4;        // [BKEY][RS]
   float* Ps = Cs + BKEY * RS;      // [BQ][BKEY]
   const int tid = threadIdx.x, i = tid >> 4, l = tid & 15;
-  const int h = blockIdx.y;
   const int* tile = p.tiles + 4 * blockIdx.x;
-  const int row0 = tile[0], n = tile[1], pos0 = tile[2], slot = tile[3];
+  // kHeadRows (decoded tokens): the 16 rows of the tile are 16 HEADS of one token, which all attend to
+  // the same latent rows, so a block of keys is loaded once for all of them; the keys are dealt to
+  // gridDim.z CTAs and merged afterwards.  Otherwise: 16 consecutive tokens of one sequence, one head.
+  const int h0 = kHeadRows ? blockIdx.y * BQ : blockIdx.y;
+  const int h = kHeadRows ? h0 + i : h0;
+  const int row0 = tile[0], pos0 = tile[2], slot = tile[3];
+  const int n = kHeadRows ? min(BQ, p.H - h0) : tile[1];
+  const int split = kHeadRows ? blockIdx.z : 0, nsplit = kHeadRows ? p.nsplit : 1;
   const int32_t* pt = p.page_tables + static_cast<size_t>(slot) * p.pt_stride;
   const size_t ldq = static_cast<size_t>(p.H) * R;
   for (int idx = tid; idx < BQ * R4; idx += kThreads) {
     const int qi = idx / R4, k = idx % R4;
-    Qs[idx] = (qi < n && k < R) ? p.q[(row0 + qi) * ldq + static_cast<size_t>(h) * R + k] * p.scale : 0.f;
+    const size_t src = kHeadRows ? row0 * ldq + static_cast<size_t>(h0 + qi) * R + k
+                                 : (row0 + qi) * ldq + static_cast<size_t>(h0) * R + k;
+    Qs[idx] = (qi < n && k < R) ? p.q[src] * p.scale : 0.f;
   }
-  float m = p.sink ? p.sink[h] : kNegBig;
-  float lsum = p.sink ? 1.0f : 0.0f;
+  const bool has_sink = p.sink != nullptr && split == 0 && i < n;   // the sink belongs to split 0
+  float m = has_sink ? p.sink[h] : kNegBig;
+  float lsum = has_sink ? 1.0f : 0.0f;
   float4 acc[KK4];
 #pragma unroll
   for (int kk = 0; kk < KK4; ++kk) acc[kk] = make_float4(0.f, 0.f, 0.f, 0.f);
-  const int nkeys = pos0 + n;
-  const int my_last = pos0 + i;  // last visible key of query i
-  for (int j0 = 0; j0 < nkeys; j0 += BKEY) {
+  const int nkeys = kHeadRows ? pos0 + 1 : pos0 + n;
+  const int my_last = kHeadRows ? pos0 : pos0 + i;  // last visible key of query i
+  for (int j0 = split * BKEY; j0 < nkeys; j0 += nsplit * BKEY) {
     __syncthreads();  // Qs ready (first pass) / previous block consumed
     load_latent_block(Cs, RS, R4, p.cache, p.cache_dtype, pt, p.page, j0, nkeys, R);
     __syncthreads();
@@ -151,8 +163,26 @@ __global__ void __launch_bounds__(kThreads) latent_attn_tile_kernel(const vila_l
       }
     }
   }
+  if (kHeadRows && nsplit > 1) {
+    if (i < n) {   // un-normalised partial of this split: R sums, then the running max and sum
+      float* part = p.partial + ((static_cast<size_t>(row0) * p.H + h) * nsplit + split) * (R + 2);
+#pragma unroll
+      for (int kk = 0; kk < KK4; ++kk) {
+        const int k = 4 * l + 64 * kk;
+        const float v[4] = {acc[kk].x, acc[kk].y, acc[kk].z, acc[kk].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (k + e < R) part[k + e] = v[e];
+      }
+      if (l == 0) {
+        part[R] = m;
+        part[R + 1] = lsum;
+      }
+    }
+    return;
+  }
   if (i < n) {
-    const size_t row = row0 + i;
+    const size_t row = kHeadRows ? row0 : row0 + i;
     float g = 1.0f / lsum;
     if (p.gate) g *= sigmoid_f(ld_any(p.gate, p.gate_dtype, row * p.ldg + h));
     const size_t ob = row * ldq + static_cast<size_t>(h) * R;
@@ -428,6 +458,27 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   VB_CHECK(p.R >= 1 && p.R <= 512, "latent_attention: latent width %d not in [1, 512]", p.R);
   VB_CHECK(p.H >= 1 && p.H <= 65535 && p.page >= 1, "latent_attention: H=%d page=%d", p.H, p.page);
   const dim3 grid(p.ntiles, p.H), block(kThreads);
+  if (p.decode && p.H >= 4) {
+    // decoded tokens, several heads: the heads of a token are the rows of a tile (one latent load for all)
+    VB_CHECK(p.nsplit >= 1 && p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
+             "latent_attention: nsplit=%d needs 1..64 and a partial buffer", p.nsplit);
+    const int r4 = round4(p.R);
+    const size_t smem = sizeof(float) * (BQ * r4 + BKEY * (r4 + 4) + BQ * BKEY);
+    const dim3 hgrid(p.ntiles, (p.H + BQ - 1) / BQ, p.nsplit), block(kThreads);
+#define VB_LAT_HEADS(KK)                                                                       \
+  do {                                                                                         \
+    if (set_smem(latent_attn_tile_kernel<KK, true>, smem)) return 2;                           \
+    VB_CUDA(launch_serial(latent_attn_tile_kernel<KK, true>, hgrid, block, smem, stream, p));  \
+  } while (0)
+    if (p.R <= 64) VB_LAT_HEADS(1);
+    else if (p.R <= 128) VB_LAT_HEADS(2);
+    else if (p.R <= 256) VB_LAT_HEADS(4);
+    else VB_LAT_HEADS(8);
+#undef VB_LAT_HEADS
+    if (p.nsplit > 1)
+      VB_CUDA(launch_serial(latent_attn_merge_kernel, dim3(p.ntiles, p.H), block, 0, stream, p));
+    return 0;
+  }
   if (p.decode) {
     int rp = 1;
     while (rp < p.R) rp <<= 1;
@@ -450,8 +501,8 @@ int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream) {
   const size_t smem = sizeof(float) * (BQ * r4 + BKEY * (r4 + 4) + BQ * BKEY);
 #define VB_LAT_TILE(KK)                                                                    \
   do {                                                                                     \
-    if (set_smem(latent_attn_tile_kernel<KK>, smem)) return 2;                             \
-    VB_CUDA(launch_serial(latent_attn_tile_kernel<KK>, grid, block, smem, stream, p));        \
+    if (set_smem(latent_attn_tile_kernel<KK, false>, smem)) return 2;                      \
+    VB_CUDA(launch_serial(latent_attn_tile_kernel<KK, false>, grid, block, smem, stream, p)); \
   } while (0)
   if (p.R <= 64) VB_LAT_TILE(1);
   else if (p.R <= 128) VB_LAT_TILE(2);
