@@ -436,6 +436,117 @@ typedef struct vila_sink_attn_params {
 } vila_sink_attn_params;
 int vila_sink_attention(const vila_sink_attn_params* p, void* stream);
 
+/* ---- blocks added for parallel-sublayer models with rotary grouped-query attention over a paged
+ * K/V pool, short input convolutions, hashed token-pair embeddings and group-limited sigmoid routing.
+ * Every mechanism is a parameterised call; nothing here is tied to one architecture. ------------- */
+
+/* vila_glinear epilogue (flags): the weight rows are interleaved (gate_0, up_0, gate_1, ...) as for
+ * VILA_FLAG_SWIGLU, out has N / 2 columns, and
+ *   g = min(z_gate, act_limit), u = clamp(z_up, -act_limit, act_limit), out = g * sigmoid(act_alpha * g) * (u + 1)
+ * act_alpha / act_limit travel in vila_glinear_ext, passed through vila_glinear_x. */
+#define VILA_FLAG_GLU_CLAMP 4
+typedef struct vila_glinear_ext {
+  float act_alpha, act_limit;
+} vila_glinear_ext;
+int vila_glinear_x(const vila_glinear_params* p, const vila_glinear_ext* x, void* stream);
+
+/* out[t, :] = table[ids[t], :] + pair_table[r(t), :] (fp32), with
+ *   r(t) = prev_ids[t] < 0 ? buckets : (prev_ids[t] * mul_prev + ids[t] * mul_cur) mod buckets
+ * (pair_table has buckets + 1 rows; the last one serves tokens without a predecessor). */
+int vila_embed_pair_rows(const void* table, int table_dtype, const void* pair_table, int pair_dtype,
+                         const int32_t* ids, const int32_t* prev_ids, int64_t mul_prev, int64_t mul_cur,
+                         int64_t buckets, float* out, int rows, int cols, void* stream);
+
+/* x[r, :] += vec  (fp32 stream, vec of any dtype) */
+int vila_add_row_vector(float* x, const void* vec, int vec_dtype, int rows, int cols, void* stream);
+
+/* RMS norm in `groups` equal consecutive pieces of every row, each with its own root mean square:
+ *   out[r, c] = x[r, c] / sqrt(mean_{c' in piece(c)} x[r, c']^2 + eps) * (w[c] + w_offset) */
+int vila_group_rmsnorm_rows(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype,
+                            float w_offset, float eps, void* out, int out_dtype, int64_t ldo, int rows,
+                            int cols, int groups, void* stream);
+
+/* Causal short convolution over time on every channel of ragged rows, with the input added back:
+ *   out[t, c] = h[t, c] + sum_{j < taps} w[c, j] * h[t - (taps - 1) + j, c]
+ * where rows before a sequence's portion come from its state slot (the last taps - 1 inputs of the
+ * sequence, fp32 [slots, taps - 1, cols], oldest first) and rows before position 0 are zero.
+ * row_seq[t] names the sequence of row t in seqs [nseq, 4] = (first row, rows, first position, slot).
+ * vila_short_conv_state then stores the last taps - 1 inputs of every sequence (call it after the
+ * convolution of the same step: it overwrites what the convolution reads). */
+int vila_short_conv_rows(const float* h, const void* w, int w_dtype, const float* state,
+                         const int32_t* seqs, const int32_t* row_seq, void* out, int out_dtype,
+                         int rows, int cols, int taps, void* stream);
+int vila_short_conv_state(const float* h, float* state, const int32_t* seqs, int nseq, int cols, int taps,
+                          void* stream);
+
+/* Rotary positions + unit norm + cache append for grouped-query attention.  qkv [T, ldq] holds q (H
+ * heads of dim) | k (G heads of dim) | v (G heads of vdim).  On the first rot_dims columns of every q
+ * and k head the pairs (2i, 2i+1) turn by positions[t] * inv_freq[i] (inv_freq fp64 [rot_dims / 2]);
+ * then, if unit_norm, every q and k head is divided by sqrt(mean(head^2) + eps).
+ *   q_out fp32 [T, H * dim];  pool row cache_rows[t] = k (G * dim) | v (G * vdim) in pool_dtype. */
+typedef struct vila_rope_append_params {
+  const void* qkv;
+  int64_t ldq;
+  const int32_t* positions;
+  const int32_t* cache_rows;
+  const double* inv_freq;
+  float* q_out;
+  void* pool;
+  int32_t qkv_dtype, pool_dtype, T, H, G, dim, vdim, rot_dims, unit_norm;
+  float eps;
+} vila_rope_append_params;
+int vila_rope_append(const vila_rope_append_params* p, void* stream);
+
+/* vila_paged_attention — causal grouped-query attention over a paged pool whose rows are
+ * k (G * dim) | v (G * vdim) per token, fp32 scores / softmax / weighted sum:
+ *   s_h(i, j) = scale * <q_h(i), k_{h / (H / G)}(j)>;  if talk: s_h <- sum_g talk[h, g] s_g (all H heads
+ *   of a (query, key) pair are mixed before the softmax);  j <= pos(i)
+ *   p_h(i, j) = exp(s_h) / (sum_j exp(s_h) + exp(sink[h]))      (sink == NULL: ordinary softmax)
+ *   out_h(i) = sum_j p_h(i, j) v_{h / (H / G)}(j)
+ * tiles [ntiles, 4] = (first batch row, rows (<= 16), position of the first row, slot); page tables as
+ * in vila_latent_attention.  nsplit > 1 (tiles of ONE row only: decoded tokens) deals the key blocks of
+ * a row to nsplit CTAs; partial is fp32 [T, nsplit, H, vdim + 2], caller-owned. */
+typedef struct vila_paged_attn_params {
+  const float* q; /* [T, H * dim] */
+  const void* pool;
+  const int32_t* page_tables;
+  const int32_t* tiles;
+  const float* talk; /* [H, H] or NULL */
+  const float* sink; /* [H] or NULL */
+  void* out;         /* [T, H * vdim] */
+  float* partial;
+  int32_t pool_dtype, out_dtype, ntiles, pt_stride, H, G, dim, vdim, page, nsplit;
+  int32_t max_rows; /* largest row count of any tile (1: decoded tokens only) */
+  float scale;
+} vila_paged_attn_params;
+int vila_paged_attention(const vila_paged_attn_params* p, void* stream);
+
+/* Router with sigmoid scores and group-limited choice: s = sigmoid(w_router x) (fp32), choice = s +
+ * correction; the experts form `groups` equal groups of neighbours, a group's score is the sum of its
+ * two largest choice values (its only one if groups == experts), only experts of the `keep` best groups
+ * can be chosen; the `top` largest choice values win (ties: the lower index); weight = s of the chosen
+ * (not renormalised).  correction may be NULL.  idx / weight are [rows, top]. */
+int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float* w_router,
+                           const float* correction, int32_t* idx, float* weight, int rows, int cols,
+                           int experts, int top, int groups, int keep, void* stream);
+
+/* x[r, :] += mult * (a[r, :] + sum_{j < n_partials} part[r * n_partials + j, :])  (a or part may be NULL) */
+int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,
+                           int part_dtype, int64_t ldp, int n_partials, float mult, int rows, int cols,
+                           void* stream);
+
+/* vila_gated_norm_residual with the update multiplied by `mult` */
+int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
+                                    const void* gate, int gate_dtype, int64_t ldg, const void* gate_bias,
+                                    int bias_dtype, const void* w, int w_dtype, float w_offset, float eps,
+                                    float mult, int rows, int cols, void* stream);
+
+/* out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]   (z fp32 [T, cols]; a per-token side input
+ * gated by a projection of the stream) */
+int vila_gelu_mul_gather(const float* z, const void* table, int table_dtype, int64_t ld_table,
+                         const int32_t* ids, int col0, void* out, int out_dtype, int rows, int cols,
+                         void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -111,6 +111,30 @@ class Hgrn2Params(C.Structure):
     ]
 
 
+class GLinearExt(C.Structure):
+    _fields_ = [("act_alpha", c_float), ("act_limit", c_float)]
+
+
+class RopeAppendParams(C.Structure):
+    _fields_ = [
+        ("qkv", c_void_p), ("ldq", c_i64), ("positions", c_void_p), ("cache_rows", c_void_p),
+        ("inv_freq", c_void_p), ("q_out", c_void_p), ("pool", c_void_p),
+        ("qkv_dtype", C.c_int32), ("pool_dtype", C.c_int32), ("T", C.c_int32), ("H", C.c_int32),
+        ("G", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("rot_dims", C.c_int32),
+        ("unit_norm", C.c_int32), ("eps", c_float),
+    ]
+
+
+class PagedAttnParams(C.Structure):
+    _fields_ = [
+        ("q", c_void_p), ("pool", c_void_p), ("page_tables", c_void_p), ("tiles", c_void_p),
+        ("talk", c_void_p), ("sink", c_void_p), ("out", c_void_p), ("partial", c_void_p),
+        ("pool_dtype", C.c_int32), ("out_dtype", C.c_int32), ("ntiles", C.c_int32), ("pt_stride", C.c_int32),
+        ("H", C.c_int32), ("G", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("page", C.c_int32),
+        ("nsplit", C.c_int32), ("max_rows", C.c_int32), ("scale", c_float),
+    ]
+
+
 # name -> argtypes; every function returns int (0 == ok) unless listed in _RESTYPES
 SIGNATURES = {
     "vila_abi_version": [],
@@ -161,6 +185,25 @@ SIGNATURES = {
     "vila_moe_route": [c_void_p, c_int, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                        c_int, c_void_p],
     "vila_moe_group": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "vila_glinear_x": [C.POINTER(GLinearParams), C.POINTER(GLinearExt), c_void_p],
+    "vila_embed_pair_rows": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_i64, c_i64, c_i64, c_void_p,
+                             c_int, c_int, c_void_p],
+    "vila_add_row_vector": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "vila_group_rmsnorm_rows": [c_void_p, c_int, c_i64, c_void_p, c_int, c_float, c_float, c_void_p, c_int, c_i64,
+                                c_int, c_int, c_int, c_void_p],
+    "vila_short_conv_rows": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_int, c_void_p],
+    "vila_short_conv_state": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "vila_rope_append": [C.POINTER(RopeAppendParams), c_void_p],
+    "vila_paged_attention": [C.POINTER(PagedAttnParams), c_void_p],
+    "vila_moe_route_sigmoid": [c_void_p, c_int, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_int, c_void_p],
+    "vila_residual_add_rows": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_i64, c_int, c_float, c_int,
+                               c_int, c_void_p],
+    "vila_gated_norm_residual_scaled": [c_void_p, c_void_p, c_int, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p,
+                                        c_int, c_void_p, c_int, c_float, c_float, c_float, c_int, c_int, c_void_p],
+    "vila_gelu_mul_gather": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                             c_void_p],
 }
 _RESTYPES = {"vila_last_error": C.c_char_p}
 

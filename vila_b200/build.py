@@ -34,6 +34,8 @@ SOURCES = [
     "glinear.cu",
     "latent_attn.cu",
     "hgrn2.cu",
+    "short_conv.cu",
+    "paged_attn.cu",
 ]
 HEADERS = ["common.cuh", "kernels.h", "dtype_any.cuh", "../../include/vila_b200.h"]
 

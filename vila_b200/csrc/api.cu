@@ -388,4 +388,84 @@ int vila_moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs,
   return vb::moe_group(idx, seg, sorted, pairs, experts, st(stream));
 }
 
+int vila_glinear_x(const vila_glinear_params* p, const vila_glinear_ext* x, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::glinear(*p, st(stream), x);
+}
+
+int vila_embed_pair_rows(const void* table, int table_dtype, const void* pair_table, int pair_dtype,
+                         const int32_t* ids, const int32_t* prev_ids, int64_t mul_prev, int64_t mul_cur,
+                         int64_t buckets, float* out, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::embed_pair_rows(table, table_dtype, pair_table, pair_dtype, ids, prev_ids, mul_prev, mul_cur,
+                             buckets, out, rows, cols, st(stream));
+}
+
+int vila_add_row_vector(float* x, const void* vec, int vec_dtype, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::add_row_vector(x, vec, vec_dtype, rows, cols, st(stream));
+}
+
+int vila_group_rmsnorm_rows(const void* x, int x_dtype, int64_t ldx, const void* w, int w_dtype,
+                            float w_offset, float eps, void* out, int out_dtype, int64_t ldo, int rows,
+                            int cols, int groups, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::rmsnorm_rows(x, x_dtype, ldx, w, w_dtype, w_offset, eps, out, out_dtype, ldo, nullptr, rows, cols,
+                          st(stream), groups);
+}
+
+int vila_short_conv_rows(const float* h, const void* w, int w_dtype, const float* state,
+                         const int32_t* seqs, const int32_t* row_seq, void* out, int out_dtype,
+                         int rows, int cols, int taps, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::short_conv_rows(h, w, w_dtype, state, seqs, row_seq, out, out_dtype, rows, cols, taps, st(stream));
+}
+
+int vila_short_conv_state(const float* h, float* state, const int32_t* seqs, int nseq, int cols, int taps,
+                          void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::short_conv_state(h, state, seqs, nseq, cols, taps, st(stream));
+}
+
+int vila_rope_append(const vila_rope_append_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::rope_append(*p, st(stream));
+}
+
+int vila_paged_attention(const vila_paged_attn_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::paged_attention(*p, st(stream));
+}
+
+int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float* w_router,
+                           const float* correction, int32_t* idx, float* weight, int rows, int cols,
+                           int experts, int top, int groups, int keep, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::moe_route_sigmoid(x, x_dtype, ldx, w_router, correction, idx, weight, rows, cols, experts, top,
+                               groups, keep, st(stream));
+}
+
+int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,
+                           int part_dtype, int64_t ldp, int n_partials, float mult, int rows, int cols,
+                           void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::residual_add_rows(x, a, a_dtype, lda, part, part_dtype, ldp, n_partials, mult, rows, cols, st(stream));
+}
+
+int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
+                                    const void* gate, int gate_dtype, int64_t ldg, const void* gate_bias,
+                                    int bias_dtype, const void* w, int w_dtype, float w_offset, float eps,
+                                    float mult, int rows, int cols, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::gated_norm_residual(x, part, part_dtype, ldp, n_partials, gate, gate_dtype, ldg, gate_bias,
+                                 bias_dtype, w, w_dtype, w_offset, eps, rows, cols, st(stream), mult);
+}
+
+int vila_gelu_mul_gather(const float* z, const void* table, int table_dtype, int64_t ld_table,
+                         const int32_t* ids, int col0, void* out, int out_dtype, int rows, int cols,
+                         void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::gelu_mul_gather(z, table, table_dtype, ld_table, ids, col0, out, out_dtype, rows, cols, st(stream));
+}
+
 }  // extern "C"

@@ -18,13 +18,20 @@ namespace {
 
 constexpr int BN = 64, BK = 16, kThreads = 256;
 
+// clamped gated unit: g = min(zg, limit), u = clamp(zu, +-limit), g * sigmoid(alpha * g) * (u + 1)
+__device__ __forceinline__ float glu_clamp_f(float zg, float zu, const vila_glinear_ext& x) {
+  const float g = fminf(zg, x.act_limit), u = fminf(fmaxf(zu, -x.act_limit), x.act_limit);
+  return g * sigmoid_f(x.act_alpha * g) * (u + 1.0f);
+}
+
 // Epilogue of a thread's TM x 4 block: bias, activation (or SwiGLU over column pairs), routing weight,
 // scatter through the output row index.
 template <int TM>
-__device__ __forceinline__ void store_block(const vila_glinear_params& p, int g, int n0, int tx,
-                                            const int* orows, float (&acc)[TM][4]) {
+__device__ __forceinline__ void store_block(const vila_glinear_params& p, const vila_glinear_ext& x, int g, int n0,
+                                            int tx, const int* orows, float (&acc)[TM][4]) {
   const size_t o_col0 = p.mode == 0 ? static_cast<size_t>(g) * p.o_group_off : 0;
   const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+  const bool glu_clamp = (p.flags & VILA_FLAG_GLU_CLAMP) != 0;
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
     const int orow = orows[i];
@@ -44,7 +51,13 @@ __device__ __forceinline__ void store_block(const vila_glinear_params& p, int g,
       v[j] = z;
     }
     const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
-    if (swiglu) {
+    if (glu_clamp) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + tx * 4 + 2 * j;
+        if (n + 1 < p.N) st_any(p.out, p.out_dtype, ob + n / 2, glu_clamp_f(v[2 * j], v[2 * j + 1], x) * rs);
+      }
+    } else if (swiglu) {
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int n = n0 + tx * 4 + 2 * j;
@@ -103,7 +116,7 @@ __device__ __forceinline__ bool tile_rows(const vila_glinear_params& p, int* aro
 }
 
 template <int BM>
-__global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_params p) {
+__global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_params p, const vila_glinear_ext x) {
   constexpr int TM = BM / 16;
   __shared__ float As[BK][BM + 1];
   __shared__ __align__(16) float Ws[BK][BN];
@@ -153,7 +166,7 @@ __global__ void __launch_bounds__(kThreads) glinear_kernel(const vila_glinear_pa
     __syncthreads();
   }
 
-  store_block<TM>(p, g, n0, tx, orow_s + ty * TM, acc);
+  store_block<TM>(p, x, g, n0, tx, orow_s + ty * TM, acc);
 }
 
 // ---- bf16 operands, many rows: warp-level tensor-core tiles (wmma, fp32 accumulators) ---------------
@@ -173,7 +186,7 @@ __device__ __forceinline__ uint4 load8_bf16(const __nv_bfloat16* base, size_t of
   return *reinterpret_cast<uint4*>(t);
 }
 
-__global__ void __launch_bounds__(kThreads) glinear_wmma_kernel(const vila_glinear_params p, int vec) {
+__global__ void __launch_bounds__(kThreads) glinear_wmma_kernel(const vila_glinear_params p, const vila_glinear_ext x, int vec) {
   using namespace nvcuda;
   constexpr int BM = 64;
   __shared__ __align__(32) __nv_bfloat16 As[BM][WLD];
@@ -224,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) glinear_wmma_kernel(const vila_gline
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = Cs[ty * 4 + i][tx * 4 + j];
-  store_block<4>(p, g, n0, tx, orow_s + ty * 4, acc);
+  store_block<4>(p, x, g, n0, tx, orow_s + ty * 4, acc);
 }
 
 // ---- few rows per group (decoded tokens): weight-streaming kernel ---------------------------------
@@ -258,7 +271,7 @@ __device__ __forceinline__ float finish(const vila_glinear_params& p, float z, i
 }
 
 // vec: K % 8 == 0 and every row of A and W starts on an 8-element boundary (16 B bf16, 32 B fp32)
-__global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const vila_glinear_params p, int vec) {
+__global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const vila_glinear_params p, const vila_glinear_ext x, int vec) {
   __shared__ int arow_s[kSmallRows], orow_s[kSmallRows];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = blockIdx.y;
@@ -270,6 +283,7 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
   const size_t wb = wa + p.ldw;
   const bool has_a = n_a < p.N, has_b = n_b < p.N;
   const bool swiglu = (p.flags & VILA_FLAG_SWIGLU) != 0;
+  const bool glu_clamp = (p.flags & VILA_FLAG_GLU_CLAMP) != 0;
   for (int m0 = m_begin; m0 < m_end; m0 += kSmallRows) {
     const int nr = min(kSmallRows, m_end - m0);
     __syncthreads();
@@ -329,7 +343,9 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
         if (lane == 0 && has_a) {
           const float rs = p.row_scale ? p.row_scale[orow] : 1.0f;
           const size_t ob = static_cast<size_t>(orow) * p.ldo + o_col0;
-          if (swiglu) {
+          if (glu_clamp) {
+            if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, glu_clamp_f(finish(p, za, g, n_a), finish(p, zb, g, n_b), x) * rs);
+          } else if (swiglu) {
             if (has_b) st_any(p.out, p.out_dtype, ob + n_a / 2, silu_exact_f(finish(p, za, g, n_a)) * finish(p, zb, g, n_b) * rs);
           } else {
             st_any(p.out, p.out_dtype, ob + n_a, finish(p, za, g, n_a) * rs);
@@ -343,11 +359,13 @@ __global__ void __launch_bounds__(kSmallWarps * 32) glinear_small_kernel(const v
 
 }  // namespace
 
-int glinear(const vila_glinear_params& p, cudaStream_t stream) {
+int glinear(const vila_glinear_params& p, cudaStream_t stream, const vila_glinear_ext* ext) {
+  vila_glinear_ext x = {1.0f, INFINITY};
+  if (ext) x = *ext;
   if (p.M <= 0 || p.N <= 0) return 0;
   VB_CHECK(p.K > 0 && p.groups >= 1, "glinear: K=%d groups=%d", p.K, p.groups);
   VB_CHECK(p.mode == 0 || (p.mode == 1 && p.seg != nullptr), "glinear: mode %d needs seg", p.mode);
-  VB_CHECK(!(p.flags & VILA_FLAG_SWIGLU) || (p.N % 2 == 0 && p.act == VILA_ACT_NONE),
+  VB_CHECK(!(p.flags & (VILA_FLAG_SWIGLU | VILA_FLAG_GLU_CLAMP)) || (p.N % 2 == 0 && p.act == VILA_ACT_NONE),
            "glinear: the SwiGLU epilogue needs an even N and no other activation");
   VB_CHECK(p.a_rows == nullptr || p.a_row_div >= 1, "glinear: a_row_div=%d", p.a_row_div);
   const bool small = p.M <= 16;
@@ -359,7 +377,7 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
                      reinterpret_cast<uintptr_t>(p.w) % (8 * ew) == 0;
     const dim3 grid((p.N + 2 * kSmallWarps - 1) / (2 * kSmallWarps), p.groups);
     VB_CHECK(grid.y <= 65535, "glinear: too many groups (%d)", p.groups);
-    VB_CUDA(launch_serial(glinear_small_kernel, grid, dim3(kSmallWarps * 32), 0, stream, p, vec ? 1 : 0));
+    VB_CUDA(launch_serial(glinear_small_kernel, grid, dim3(kSmallWarps * 32), 0, stream, p, x, vec ? 1 : 0));
     return 0;
   }
   const int bm = small ? 16 : 64;
@@ -377,11 +395,11 @@ int glinear(const vila_glinear_params& p, cudaStream_t stream) {
     const bool vec = p.K % 8 == 0 && p.lda % 8 == 0 && p.ldw % 8 == 0 && p.w_group_stride % 8 == 0 &&
                      p.a_group_off % 8 == 0 && reinterpret_cast<uintptr_t>(p.a) % 16 == 0 &&
                      reinterpret_cast<uintptr_t>(p.w) % 16 == 0;
-    VB_CUDA(launch_serial(glinear_wmma_kernel, grid, dim3(kThreads), 0, stream, p, vec ? 1 : 0));
+    VB_CUDA(launch_serial(glinear_wmma_kernel, grid, dim3(kThreads), 0, stream, p, x, vec ? 1 : 0));
     return 0;
   }
-  if (small) VB_CUDA(launch_serial(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p));
-  else VB_CUDA(launch_serial(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p));
+  if (small) VB_CUDA(launch_serial(glinear_kernel<16>, grid, dim3(kThreads), 0, stream, p, x));
+  else VB_CUDA(launch_serial(glinear_kernel<64>, grid, dim3(kThreads), 0, stream, p, x));
   return 0;
 }
 

@@ -228,10 +228,26 @@ int embed_rows(const void* table, int dt, const int32_t* ids, float* out, int ro
                cudaStream_t stream);
 int rmsnorm_rows(const void* x, int x_dt, int64_t ldx, const void* w, int w_dt, float w_off, float eps,
                  void* out, int o_dt, int64_t ldo, const int32_t* out_rows, int rows, int cols,
-                 cudaStream_t stream);
+                 cudaStream_t stream, int groups = 1);
 int gated_norm_residual(float* x, const void* part, int p_dt, int64_t ldp, int np, const void* gate,
                         int g_dt, int64_t ldg, const void* gb, int b_dt, const void* w, int w_dt,
-                        float w_off, float eps, int rows, int cols, cudaStream_t stream);
+                        float w_off, float eps, int rows, int cols, cudaStream_t stream, float mult = 1.0f);
+int embed_pair_rows(const void* table, int dt, const void* pair, int pdt, const int32_t* ids,
+                    const int32_t* prev, long long mul_prev, long long mul_cur, long long buckets, float* out,
+                    int rows, int cols, cudaStream_t stream);
+int add_row_vector(float* x, const void* vec, int dt, int rows, int cols, cudaStream_t stream);
+int residual_add_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp,
+                      int np, float mult, int rows, int cols, cudaStream_t stream);
+int gelu_mul_gather(const float* z, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
+                    void* out, int o_dt, int rows, int cols, cudaStream_t stream);
+int moe_route_sigmoid(const void* x, int x_dt, int64_t ldx, const float* wr, const float* corr, int32_t* idx,
+                      float* weight, int rows, int cols, int experts, int top, int groups, int keep,
+                      cudaStream_t stream);
+int short_conv_rows(const float* h, const void* w, int w_dt, const float* state, const int32_t* seqs,
+                    const int32_t* row_seq, void* out, int o_dt, int rows, int cols, int taps,
+                    cudaStream_t stream);
+int short_conv_state(const float* h, float* state, const int32_t* seqs, int nseq, int cols, int taps,
+                     cudaStream_t stream);
 int moe_route(const void* x, int x_dt, int64_t ldx, const float* wr, const float* bias, int32_t* idx,
               float* weight, int rows, int cols, int experts, int top, cudaStream_t stream);
 int moe_group(const int32_t* idx, int32_t* seg, int32_t* sorted, int pairs, int experts,
@@ -241,10 +257,15 @@ struct vila_glinear_params;
 struct vila_latent_attn_params;
 struct vila_hgrn2_params;
 struct vila_sink_attn_params;
+struct vila_glinear_ext;
+struct vila_rope_append_params;
+struct vila_paged_attn_params;
 namespace vb {
+int rope_append(const vila_rope_append_params& p, cudaStream_t stream);
+int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream);
 int sink_attention(const vila_sink_attn_params& p, cudaStream_t stream);
 int gather_rows(const void* src, const int32_t* rows, void* dst, int n_rows, int row_bytes, cudaStream_t stream);
-int glinear(const vila_glinear_params& p, cudaStream_t stream);
+int glinear(const vila_glinear_params& p, cudaStream_t stream, const vila_glinear_ext* ext = nullptr);
 int latent_attention(const vila_latent_attn_params& p, cudaStream_t stream);
 int hgrn2_scan(const vila_hgrn2_params& p, cudaStream_t stream);
 

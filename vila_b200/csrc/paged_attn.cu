@@ -1,0 +1,318 @@
+// Grouped-query attention over a paged K/V pool for ragged batches, with the pieces a parallel-sublayer
+// decoder adds to it:
+//   rope_append_kernel   rotary positions on the first rot_dims columns of every q / k head (pairs
+//                        (2i, 2i+1), angle = position * inv_freq[i], evaluated in double so that far
+//                        positions keep their phase), optional unit norm per head (fp32), q out as fp32,
+//                        k | v appended to the pool row of the token
+//   paged_attn_kernel    fp32 scores of ALL H heads of a (query, key) pair, optional head mixing
+//                        s_h <- sum_g talk[h, g] s_g before the softmax, online softmax whose running
+//                        (max, sum) starts at (sink_h, 1) when a sink is given, fp32 weighted sum.
+//                        A CTA owns BQ consecutive rows of one sequence x all heads (BQ * H "score rows");
+//                        prompt portions use BQ up to 16, decoded tokens BQ = 1 with the key blocks of a
+//                        row dealt to nsplit CTAs
+//   paged_attn_merge_kernel  merges the nsplit partial (max, sum, weighted sum) triples of a decoded token
+// Every reduction over keys runs in key order inside a block and block by block, so a row's result does
+// not depend on what else is in the launch.
+#include "../../include/vila_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+#include "dtype_any.cuh"
+
+namespace vb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr float kNegBig = -1e30f;
+
+__host__ __device__ __forceinline__ int round4(int r) { return (r + 3) & ~3; }
+
+// ---- rotary + unit norm + append ---------------------------------------------------------------------
+// One CTA per token; warp w takes the heads w, w + 8, ... of q then k; v is copied by all threads.
+__global__ void __launch_bounds__(kThreads) rope_append_kernel(const vila_rope_append_params p) {
+  extern __shared__ float cs[];   // cos [rot/2] | sin [rot/2]
+  const int t = blockIdx.x, half = p.rot_dims >> 1;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const double pos = static_cast<double>(p.positions[t]);
+  for (int i = tid; i < half; i += kThreads) {
+    double s, c;
+    sincos(pos * p.inv_freq[i], &s, &c);
+    cs[i] = static_cast<float>(c);
+    cs[half + i] = static_cast<float>(s);
+  }
+  __syncthreads();
+  const size_t in0 = static_cast<size_t>(t) * p.ldq;
+  const size_t prow = static_cast<size_t>(p.cache_rows[t]) * (static_cast<size_t>(p.G) * (p.dim + p.vdim));
+  for (int hh = warp; hh < p.H + p.G; hh += kWarps) {
+    const bool is_q = hh < p.H;
+    const size_t src = in0 + static_cast<size_t>(hh) * p.dim;   // q heads then k heads are contiguous
+    // pass 1: rotated values -> sum of squares (recomputed in pass 2: dim is small, no buffer needed)
+    float ss = 0.f;
+    for (int c = lane; c < p.dim; c += 32) {
+      float v = ld_any(p.qkv, p.qkv_dtype, src + c);
+      if (c < p.rot_dims) {
+        const float o = ld_any(p.qkv, p.qkv_dtype, src + (c ^ 1));
+        const float co = cs[c >> 1], si = cs[half + (c >> 1)];
+        v = (c & 1) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
+      }
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = p.unit_norm ? 1.0f / sqrtf(ss / static_cast<float>(p.dim) + p.eps) : 1.0f;
+    for (int c = lane; c < p.dim; c += 32) {
+      float v = ld_any(p.qkv, p.qkv_dtype, src + c);
+      if (c < p.rot_dims) {
+        const float o = ld_any(p.qkv, p.qkv_dtype, src + (c ^ 1));
+        const float co = cs[c >> 1], si = cs[half + (c >> 1)];
+        v = (c & 1) ? fmaf(v, co, o * si) : fmaf(v, co, -(o * si));
+      }
+      v *= r;
+      if (is_q) p.q_out[(static_cast<size_t>(t) * p.H + hh) * p.dim + c] = v;
+      else st_any(p.pool, p.pool_dtype, prow + static_cast<size_t>(hh - p.H) * p.dim + c, v);
+    }
+  }
+  const size_t vsrc = in0 + static_cast<size_t>(p.H + p.G) * p.dim, vdst = prow + static_cast<size_t>(p.G) * p.dim;
+  for (int c = tid; c < p.G * p.vdim; c += kThreads)
+    st_any(p.pool, p.pool_dtype, vdst + c, ld_any(p.qkv, p.qkv_dtype, vsrc + c));
+}
+
+// ---- attention -----------------------------------------------------------------------------------------
+struct AttnShape {
+  int BQ;      // query rows per CTA
+  int BK;      // keys per block (<= 32: one lane per key in the softmax step)
+  int sub;     // CTAs per 16-row tile (grid.y)
+};
+
+__device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
+  return static_cast<size_t>(pt[j / page]) * page + (j % page);
+}
+
+// Shared memory (floats):  Qs [BQ * H][D4] (scale folded in) | Ks [BK][G][DS] | Vs [BK][G][V4] |
+//   Ss [BQ * H][BK] raw scores | Ps [BQ * H][BK] weights | talk [H * H] | m, l, alpha [BQ * H]
+// DS = D4 + 4: consecutive keys start 4 banks apart, so the float4 reads of 8 keys do not collide.
+template <int NACC>
+__global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_attn_params p, const AttnShape sh) {
+  extern __shared__ __align__(16) float sm[];
+  const int H = p.H, G = p.G, D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK;
+  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, rep = H / G;
+  float* Qs = sm;
+  float* Ks = Qs + R * D4;
+  float* Vs = Ks + BK * G * DS;
+  float* Ss = Vs + BK * G * V4;
+  float* Ps = Ss + R * BK;
+  float* Tk = Ps + R * BK;
+  float* m_s = Tk + H * H;
+  float* l_s = m_s + R;
+  float* a_s = l_s + R;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* tile = p.tiles + 4 * blockIdx.x;
+  const int i0 = blockIdx.y * BQ;
+  const int n_tile = tile[1];
+  if (i0 >= n_tile) return;
+  const int row0 = tile[0] + i0, n = min(BQ, n_tile - i0), pos0 = tile[2] + i0;
+  const int32_t* pt = p.page_tables + static_cast<size_t>(tile[3]) * p.pt_stride;
+  const int split = blockIdx.z, nsplit = gridDim.z;
+  const size_t prw = static_cast<size_t>(G) * (D + V);   // pool row width
+
+  for (int idx = tid; idx < R * D4; idx += kThreads) {
+    const int r = idx / D4, k = idx - r * D4, i = r / H, h = r - i * H;
+    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * p.scale : 0.f;
+  }
+  for (int idx = tid; idx < H * H; idx += kThreads) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
+  for (int r = tid; r < R; r += kThreads) {
+    const bool first = split == 0 && p.sink != nullptr;
+    m_s[r] = first ? p.sink[r % H] : kNegBig;
+    l_s[r] = first ? 1.0f : 0.0f;
+  }
+  float4 acc[NACC];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) acc[a] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int vq = V4 >> 2;                 // float4 columns of a head
+  const int nout = R * vq;                // float4 accumulators of the CTA: index o -> (r, c4)
+  const int nkeys = pos0 + n;             // keys 0 .. nkeys - 1 are visible to the last row
+  const int nblocks = (nkeys + BK - 1) / BK;
+
+  for (int b = split; b < nblocks; b += nsplit) {
+    const int j0 = b * BK;
+    __syncthreads();
+    // K | V rows of the block, widened to fp32; one warp per key
+    for (int jj = warp; jj < BK; jj += kWarps) {
+      const int j = j0 + jj;
+      float* kd = Ks + jj * G * DS;
+      float* vd = Vs + jj * G * V4;
+      if (j >= nkeys) {
+        for (int x = lane; x < G * DS; x += 32) kd[x] = 0.f;
+        for (int x = lane; x < G * V4; x += 32) vd[x] = 0.f;
+        continue;
+      }
+      const size_t src = pool_row(pt, p.page, j) * prw;
+      for (int x = lane; x < G * D4; x += 32) {
+        const int g = x / D4, k = x - g * D4;
+        kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + static_cast<size_t>(g) * D + k) : 0.f;
+      }
+      const size_t vsrc = src + static_cast<size_t>(G) * D;
+      for (int x = lane; x < G * V4; x += 32) {
+        const int g = x / V4, k = x - g * V4;
+        vd[x] = k < V ? ld_any(p.pool, p.pool_dtype, vsrc + static_cast<size_t>(g) * V + k) : 0.f;
+      }
+    }
+    __syncthreads();
+    // raw scores of every (score row, key)
+    for (int idx = tid; idx < R * BK; idx += kThreads) {
+      const int r = idx / BK, jj = idx - r * BK, h = r % H;
+      const float4* qr = reinterpret_cast<const float4*>(Qs + r * D4);
+      const float4* kr = reinterpret_cast<const float4*>(Ks + (jj * G + h / rep) * DS);
+      float s = 0.f;
+#pragma unroll 4
+      for (int k = 0; k < (D4 >> 2); ++k) {
+        const float4 a = qr[k], c = kr[k];
+        s = fmaf(a.x, c.x, s); s = fmaf(a.y, c.y, s); s = fmaf(a.z, c.z, s); s = fmaf(a.w, c.w, s);
+      }
+      Ss[idx] = s;
+    }
+    __syncthreads();
+    // head mixing + mask + online softmax: a warp per score row, a lane per key
+    for (int r = warp; r < R; r += kWarps) {
+      const int i = r / H, h = r - i * H;
+      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i;
+      float s = 0.f;
+      if (lane < BK) {
+        const float* tk = Tk + h * H;
+        const float* sr = Ss + (i * H) * BK + lane;
+        for (int g = 0; g < H; ++g) s = fmaf(tk[g], sr[g * BK], s);
+      }
+      s = valid ? s : kNegBig;
+      const float m_old = m_s[r];
+      const float m_new = fmaxf(m_old, warp_max(s));
+      const float pj = valid ? expf(s - m_new) : 0.f;
+      const float ps = warp_sum(pj);
+      if (lane < BK) Ps[r * BK + lane] = pj;
+      if (lane == 0) {
+        const float alpha = expf(m_old - m_new);
+        a_s[r] = alpha;
+        l_s[r] = l_s[r] * alpha + ps;
+        m_s[r] = m_new;
+      }
+    }
+    __syncthreads();
+    // weighted sum of the values
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int o = tid + a * kThreads;
+      if (o < nout) {
+        const int r = o / vq, c4 = o - r * vq, h = r % H;
+        const float alpha = a_s[r];
+        float4 v = acc[a];
+        v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
+        const float* pr = Ps + r * BK;
+        const float* vr = Vs + (h / rep) * V4 + 4 * c4;
+        for (int jj = 0; jj < BK; ++jj) {
+          const float pj = pr[jj];
+          const float4 c = *reinterpret_cast<const float4*>(vr + jj * G * V4);
+          v.x = fmaf(pj, c.x, v.x); v.y = fmaf(pj, c.y, v.y); v.z = fmaf(pj, c.z, v.z); v.w = fmaf(pj, c.w, v.w);
+        }
+        acc[a] = v;
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+    const int o = tid + a * kThreads;
+    if (o >= nout) continue;
+    const int r = o / vq, c4 = o - r * vq, i = r / H, h = r - i * H;
+    if (i >= n) continue;
+    const float v[4] = {acc[a].x, acc[a].y, acc[a].z, acc[a].w};
+    if (nsplit == 1) {
+      const float inv = 1.0f / l_s[r];
+      const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (4 * c4 + e < V) st_any(p.out, p.out_dtype, ob + e, v[e] * inv);
+    } else {
+      float* part = p.partial + ((static_cast<size_t>(row0 + i) * nsplit + split) * H + h) * (V + 2);
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (4 * c4 + e < V) part[4 * c4 + e] = v[e];
+      if (c4 == 0) { part[V] = m_s[r]; part[V + 1] = l_s[r]; }
+    }
+  }
+}
+
+// one CTA per (decoded row, head): combine the nsplit partial triples in split order
+__global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_attn_params p) {
+  const int* tile = p.tiles + 4 * blockIdx.x;
+  const int row = tile[0], h = blockIdx.y, V = p.vdim, ns = p.nsplit;
+  const float* part = p.partial + (static_cast<size_t>(row) * ns * p.H + h) * (V + 2);
+  const size_t stride = static_cast<size_t>(p.H) * (V + 2);
+  float mx = kNegBig;
+  for (int s = 0; s < ns; ++s) mx = fmaxf(mx, part[s * stride + V]);
+  float den = 0.f;
+  for (int s = 0; s < ns; ++s) den += expf(part[s * stride + V] - mx) * part[s * stride + V + 1];
+  const float inv = 1.0f / den;
+  for (int k = threadIdx.x; k < V; k += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < ns; ++s) a += expf(part[s * stride + V] - mx) * part[s * stride + k];
+    st_any(p.out, p.out_dtype, (static_cast<size_t>(row) * p.H + h) * V + k, a * inv);
+  }
+}
+
+size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK) {
+  const int D4 = round4(p.dim), V4 = round4(p.vdim), R = BQ * p.H;
+  return sizeof(float) * (static_cast<size_t>(R) * D4 + static_cast<size_t>(BK) * p.G * (D4 + 4) +
+                          static_cast<size_t>(BK) * p.G * V4 + 2 * static_cast<size_t>(R) * BK + p.H * p.H + 3 * R);
+}
+
+}  // namespace
+
+int rope_append(const vila_rope_append_params& p, cudaStream_t stream) {
+  if (p.T <= 0) return 0;
+  VB_CHECK(p.H >= 1 && p.G >= 1 && p.dim >= 1 && p.vdim >= 1 && p.rot_dims >= 0 && p.rot_dims <= p.dim &&
+               p.rot_dims % 2 == 0 && (p.rot_dims == 0 || p.inv_freq != nullptr),
+           "rope_append: H=%d G=%d dim=%d vdim=%d rot_dims=%d", p.H, p.G, p.dim, p.vdim, p.rot_dims);
+  VB_CUDA(launch_serial(rope_append_kernel, dim3(p.T), dim3(kThreads), sizeof(float) * (p.rot_dims + 2), stream, p));
+  return 0;
+}
+
+int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
+  if (p.ntiles <= 0) return 0;
+  VB_CHECK(p.H >= 1 && p.G >= 1 && p.H % p.G == 0 && p.dim >= 1 && p.vdim >= 1 && p.page >= 1 && p.nsplit >= 1 &&
+               p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
+           "paged_attention: H=%d G=%d dim=%d vdim=%d page=%d nsplit=%d", p.H, p.G, p.dim, p.vdim, p.page, p.nsplit);
+  // rows per CTA: about 64 score rows (BQ * H); decoded tokens (nsplit given) are one-row tiles
+  constexpr size_t kSmemMax = 200 * 1024;
+  AttnShape sh;
+  VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
+           "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
+  sh.BQ = 1;
+  while (sh.BQ < p.max_rows) sh.BQ <<= 1;
+  while (sh.BQ > 1 && sh.BQ * p.H > 64) sh.BQ >>= 1;
+  sh.BK = 32;
+  while (attn_smem(p, sh.BQ, sh.BK) > kSmemMax && sh.BK > 4) sh.BK >>= 1;
+  while (attn_smem(p, sh.BQ, sh.BK) > kSmemMax && sh.BQ > 1) sh.BQ >>= 1;
+  const size_t smem = attn_smem(p, sh.BQ, sh.BK);
+  VB_CHECK(smem <= kSmemMax, "paged_attention: H=%d G=%d dim=%d vdim=%d need %zu bytes of shared memory", p.H, p.G,
+           p.dim, p.vdim, smem);
+  sh.sub = (p.max_rows + sh.BQ - 1) / sh.BQ;
+  const int nacc = (sh.BQ * p.H * (round4(p.vdim) >> 2) + kThreads - 1) / kThreads;
+  VB_CHECK(nacc <= 16, "paged_attention: H=%d vdim=%d: %d accumulators per thread", p.H, p.vdim, nacc);
+  const dim3 grid(p.ntiles, sh.sub, p.nsplit);
+#define VB_PAGED(N)                                                                                              \
+  do {                                                                                                           \
+    if (smem > 48 * 1024)                                                                                        \
+      VB_CUDA(cudaFuncSetAttribute(paged_attn_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                   static_cast<int>(smem)));                                                     \
+    VB_CUDA(launch_serial(paged_attn_kernel<N>, grid, dim3(kThreads), smem, stream, p, sh));                     \
+  } while (0)
+  if (nacc <= 1) VB_PAGED(1);
+  else if (nacc <= 2) VB_PAGED(2);
+  else if (nacc <= 4) VB_PAGED(4);
+  else if (nacc <= 8) VB_PAGED(8);
+  else VB_PAGED(16);
+#undef VB_PAGED
+  if (p.nsplit > 1)
+    VB_CUDA(launch_serial(paged_attn_merge_kernel, dim3(p.ntiles, p.H), dim3(128), 0, stream, p));
+  return 0;
+}
+
+}  // namespace vb

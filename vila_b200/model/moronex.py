@@ -176,6 +176,8 @@ class MoronexForCausalLM:
     """Weights + the per-step compute of the architecture.  Sequences, pages, state slots, batching and
     sampling belong to `vila_b200.serving.TokenEngine`, which calls `forward_step` / `logits`."""
 
+    unfolds_attention = True   # the engine may hand large prompt portions over as kv_tiles / ctx_rows
+
     def __init__(self, cfg: MoronexConfig, device="cuda", dtype=torch.bfloat16):
         assert dtype in (torch.bfloat16, torch.float32)
         self.config, self.device, self.dtype = cfg, torch.device(device), dtype

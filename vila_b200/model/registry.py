@@ -8,9 +8,10 @@ from typing import Dict, Optional
 
 import torch
 
+from .lufatar import LufatarForCausalLM
 from .moronex import MoronexForCausalLM
 
-LANGUAGE_MODELS: Dict[str, type] = {"Moronex": MoronexForCausalLM}
+LANGUAGE_MODELS: Dict[str, type] = {"Moronex": MoronexForCausalLM, "Lufatar": LufatarForCausalLM}
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
 

@@ -6,7 +6,7 @@ every operation below is one call into libvila_b200.so.  No function here has an
 from __future__ import annotations
 
 import ctypes as C
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Tuple
 
 import torch
 
@@ -431,15 +431,23 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
 
 def rmsnorm_rows(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, w_offset: float = 0.0,
                  out: Optional[torch.Tensor] = None, out_dtype=None,
-                 out_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out_rows: Optional[torch.Tensor] = None, groups: int = 1) -> torch.Tensor:
     """x [rows, cols] (row stride arbitrary) -> x / sqrt(mean(x^2) + eps) * (w + w_offset).  out_rows
-    (int32 [rows]) scatters the result rows into `out` (a paged pool viewed as [pool rows, cols])."""
+    (int32 [rows]) scatters the result rows into `out` (a paged pool viewed as [pool rows, cols]).
+    groups > 1: every one of `groups` equal consecutive pieces of a row has its own root mean square."""
     assert x.dim() == 2 and x.stride(1) == 1
     rows, cols = x.shape
     if out is None:
         assert out_rows is None
         out = torch.empty(rows, cols, dtype=out_dtype or x.dtype, device=x.device)
     assert out.dim() == 2 and out.stride(1) == 1 and out.shape[1] == cols
+    if groups != 1:
+        assert out_rows is None and cols % groups == 0
+        check(_lib.load().vila_group_rmsnorm_rows(_p(x), _dt(x, "x"), x.stride(0), _p(w),
+                                                  _dt(w, "w") if w is not None else 0, w_offset, eps, _p(out),
+                                                  _dt(out, "out"), out.stride(0), rows, cols, groups, _stream()),
+              "vila_group_rmsnorm_rows")
+        return out
     check(_lib.load().vila_rmsnorm_rows(_p(x), _dt(x, "x"), x.stride(0), _p(w), _dt(w, "w") if w is not None else 0,
                                         w_offset, eps, _p(out), _dt(out, "out"), out.stride(0),
                                         _i32(out_rows, "out_rows"), rows, cols, _stream()), "vila_rmsnorm_rows")
@@ -448,19 +456,20 @@ def rmsnorm_rows(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, *, w_of
 
 def gated_norm_residual(x: torch.Tensor, part: torch.Tensor, *, n_partials: int = 1,
                         gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None,
-                        w: Optional[torch.Tensor] = None, w_offset: float = 0.0, eps: float = 1e-6) -> None:
-    """x (fp32 [rows, cols], in place) += rmsnorm(sum_j part[r * n_partials + j] * sigmoid(gate + bias)) * (w + w_offset)."""
+                        w: Optional[torch.Tensor] = None, w_offset: float = 0.0, eps: float = 1e-6,
+                        mult: float = 1.0) -> None:
+    """x (fp32 [rows, cols], in place) += mult * rmsnorm(sum_j part[r * n_partials + j] * sigmoid(gate + bias)) * (w + w_offset)."""
     assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
     rows, cols = x.shape
     assert part.dim() == 2 and part.stride(1) == 1 and part.shape == (rows * n_partials, cols)
     if gate is not None:
         assert gate.shape == (rows, cols) and gate.stride(1) == 1
-    check(_lib.load().vila_gated_norm_residual(
+    check(_lib.load().vila_gated_norm_residual_scaled(
         _p(x), _p(part), _dt(part, "part"), part.stride(0), n_partials,
         _p(gate), _dt(gate, "gate") if gate is not None else 0, gate.stride(0) if gate is not None else 0,
         _p(gate_bias), _dt(gate_bias, "gate_bias") if gate_bias is not None else 0,
-        _p(w), _dt(w, "w") if w is not None else 0, w_offset, eps, rows, cols, _stream()),
-        "vila_gated_norm_residual")
+        _p(w), _dt(w, "w") if w is not None else 0, w_offset, eps, mult, rows, cols, _stream()),
+        "vila_gated_norm_residual_scaled")
 
 
 def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = None, out_dtype=None,
@@ -468,7 +477,7 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
             groups: int = 1, a_group_off: int = 0, o_group_off: int = 0,
             seg: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None, a_row_div: int = 1,
             o_rows: Optional[torch.Tensor] = None, row_scale: Optional[torch.Tensor] = None,
-            out_rows_total: Optional[int] = None) -> torch.Tensor:
+            out_rows_total: Optional[int] = None, glu_clamp: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     """Any-shape (grouped) linear layer, fp32 accumulation on the CUDA cores (vila_glinear).
     w [N, K] (groups == 1) or [groups, N, K].  Batched groups (seg None): group g reads the A columns
     [g * a_group_off, + K) and writes the output columns [g * o_group_off, + N).  Segmented (seg int32
@@ -478,7 +487,7 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         w = w[None]
     assert w.dim() == 3 and w.stride(2) == 1 and w.shape[0] == groups, (w.shape, groups)
     N, K = w.shape[1], w.shape[2]
-    n_out = N // 2 if swiglu else N
+    n_out = N // 2 if (swiglu or glu_clamp is not None) else N   # glu_clamp = (alpha, limit): see VILA_FLAG_GLU_CLAMP
     M = a.shape[0] if a_rows is None else a_rows.numel()
     if out is None:
         cols = n_out if seg is not None or groups == 1 else o_group_off * (groups - 1) + n_out
@@ -499,8 +508,12 @@ def glinear(a: torch.Tensor, w: torch.Tensor, *, out: Optional[torch.Tensor] = N
         assert bias.dtype == w.dtype
     p.M, p.N, p.K, p.groups = M, N, K, groups
     p.mode = 0 if seg is None else 1
-    p.a_row_div, p.act, p.flags = a_row_div, act, 1 if swiglu else 0
-    check(_lib.load().vila_glinear(C.byref(p), _stream()), "vila_glinear")
+    p.a_row_div, p.act, p.flags = a_row_div, act, (1 if swiglu else 0) | (4 if glu_clamp is not None else 0)
+    if glu_clamp is not None:
+        ext = _lib.GLinearExt(float(glu_clamp[0]), float(glu_clamp[1]))
+        check(_lib.load().vila_glinear_x(C.byref(p), C.byref(ext), _stream()), "vila_glinear_x")
+    else:
+        check(_lib.load().vila_glinear(C.byref(p), _stream()), "vila_glinear")
     return out
 
 
@@ -609,4 +622,157 @@ def sink_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tiles: tor
     p.gate_dtype = _dt(gate, "gate") if gate is not None else 0
     p.ntiles, p.H, p.dim, p.vdim, p.scale = tiles.shape[0], heads, dim, vdim, scale
     check(_lib.load().vila_sink_attention(C.byref(p), _stream()), "vila_sink_attention")
+    return out
+
+
+# ---- parallel-sublayer decoders: pair embedding, short convolution, rotary GQA over a paged pool, sigmoid router ----
+def linear_any(x: torch.Tensor, w: torch.Tensor, *, swiglu: bool = False, out_dtype=None) -> torch.Tensor:
+    """x [M, K] · w[N, K]^T: bf16 operands with 16-byte aligned rows go to the tcgen05 GEMM, everything
+    else (fp32 tensors, odd shapes, an fp32 result) to the CUDA-core grouped kernel."""
+    N, K = w.shape
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and out_dtype in (None, torch.bfloat16)
+            and K % 8 == 0 and N % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and (not swiglu or N % 32 == 0)):
+        return linear(x, w, swiglu=swiglu, static_w=True)
+    return glinear(x, w, swiglu=swiglu, out_dtype=out_dtype)
+
+
+def embed_pair_rows(table: torch.Tensor, pair_table: torch.Tensor, ids: torch.Tensor, prev_ids: torch.Tensor,
+                    mul_prev: int, mul_cur: int, buckets: int) -> torch.Tensor:
+    """fp32 rows table[ids] + pair_table[(prev * mul_prev + id * mul_cur) mod buckets]; a token whose
+    prev id is negative (the first of its sequence) reads row `buckets` of pair_table."""
+    assert pair_table.shape == (buckets + 1, table.shape[1]) and table.is_contiguous() and pair_table.is_contiguous()
+    out = torch.empty(ids.numel(), table.shape[1], dtype=torch.float32, device=table.device)
+    check(_lib.load().vila_embed_pair_rows(_p(table), _dt(table, "table"), _p(pair_table), _dt(pair_table, "pair_table"),
+                                           _i32(ids, "ids"), _i32(prev_ids, "prev_ids"), mul_prev, mul_cur, buckets,
+                                           _p(out), ids.numel(), table.shape[1], _stream()), "vila_embed_pair_rows")
+    return out
+
+
+def add_row_vector(x: torch.Tensor, vec: torch.Tensor) -> None:
+    """x fp32 [rows, cols] (in place) += vec [cols]"""
+    assert x.dtype == torch.float32 and x.is_contiguous() and vec.is_contiguous() and vec.numel() == x.shape[1]
+    check(_lib.load().vila_add_row_vector(_p(x), _p(vec), _dt(vec, "vec"), x.shape[0], x.shape[1], _stream()),
+          "vila_add_row_vector")
+
+
+def short_conv_rows(h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], seqs: torch.Tensor,
+                    row_seq: torch.Tensor, *, out_dtype=None, update_state: bool = True) -> torch.Tensor:
+    """h fp32 [T, C] -> h + causal convolution over time with w [C, taps]; state fp32 [slots, taps - 1, C]
+    holds every sequence's last taps - 1 inputs (read for the taps that reach before the portion, then
+    replaced by this portion's last inputs); seqs int32 [n, 4] = (row0, rows, pos0, slot), row_seq int32 [T]."""
+    assert h.dtype == torch.float32 and h.is_contiguous() and h.dim() == 2
+    T, Cc = h.shape
+    taps = w.shape[1]
+    assert w.shape == (Cc, taps) and w.is_contiguous()
+    if taps > 1:
+        assert state is not None and state.dtype == torch.float32 and state.is_contiguous() and \
+            tuple(state.shape[1:]) == (taps - 1, Cc)
+    out = torch.empty(T, Cc, dtype=out_dtype or h.dtype, device=h.device)
+    lib = _lib.load()
+    check(lib.vila_short_conv_rows(_p(h), _p(w), _dt(w, "w"), _p(state), _i32(seqs, "seqs"), _i32(row_seq, "row_seq"),
+                                   _p(out), _dt(out, "out"), T, Cc, taps, _stream()), "vila_short_conv_rows")
+    if update_state and taps > 1:
+        check(lib.vila_short_conv_state(_p(h), _p(state), _i32(seqs, "seqs"), seqs.shape[0], Cc, taps, _stream()),
+              "vila_short_conv_state")
+    return out
+
+
+def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor, pool: torch.Tensor, *,
+                heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],
+                unit_norm: bool, eps: float) -> torch.Tensor:
+    """qkv [T, >= heads*dim + kv_heads*(dim+vdim)] -> q fp32 [T, heads*dim] (rotated, unit-normed); the
+    token's k | v go to row cache_rows[t] of pool [pool rows, kv_heads*(dim+vdim)].  inv_freq float64
+    [rot_dims / 2] (None: no rotation)."""
+    assert qkv.dim() == 2 and qkv.stride(1) == 1 and qkv.shape[1] >= heads * dim + kv_heads * (dim + vdim)
+    assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == kv_heads * (dim + vdim)
+    T = qkv.shape[0]
+    q = torch.empty(T, heads * dim, dtype=torch.float32, device=qkv.device)
+    p = _lib.RopeAppendParams()
+    p.qkv, p.ldq = _p(qkv), qkv.stride(0)
+    p.positions, p.cache_rows = _i32(positions, "positions"), _i32(cache_rows, "cache_rows")
+    if inv_freq is not None:
+        assert inv_freq.dtype == torch.float64 and inv_freq.is_cuda and inv_freq.is_contiguous()
+    p.inv_freq = _p(inv_freq)
+    p.q_out, p.pool = _p(q), _p(pool)
+    p.qkv_dtype, p.pool_dtype = _dt(qkv, "qkv"), _dt(pool, "pool")
+    p.T, p.H, p.G, p.dim, p.vdim = T, heads, kv_heads, dim, vdim
+    p.rot_dims = 0 if inv_freq is None else 2 * inv_freq.numel()
+    p.unit_norm, p.eps = 1 if unit_norm else 0, eps
+    check(_lib.load().vila_rope_append(C.byref(p), _stream()), "vila_rope_append")
+    return q
+
+
+def paged_attention(q: torch.Tensor, pool: torch.Tensor, page_tables: torch.Tensor, tiles: torch.Tensor, *,
+                    heads: int, kv_heads: int, dim: int, vdim: int, page: int, scale: float,
+                    talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None, out_dtype=None, max_rows: int = 16,
+                    nsplit: int = 1) -> torch.Tensor:
+    """Causal grouped-query attention of q fp32 [T, heads*dim] over the paged k | v pool, fp32 scores and
+    softmax, optional mixing of the heads' scores (talk fp32 [heads, heads]) and per-head sink logit in
+    the denominator.  tiles int32 [n, 4] = (row0, rows <= max_rows, pos0, slot) -> [T, heads*vdim].
+    nsplit > 1 (one-row tiles only) spreads the keys of a row over nsplit CTAs + a merge kernel."""
+    assert q.dtype == torch.float32 and q.is_contiguous() and q.shape[1] == heads * dim
+    assert pool.dim() == 2 and pool.is_contiguous() and pool.shape[1] == kv_heads * (dim + vdim)
+    if out is None:
+        out = torch.empty(q.shape[0], heads * vdim, dtype=out_dtype or pool.dtype, device=q.device)
+    assert out.shape == (q.shape[0], heads * vdim) and out.is_contiguous()
+    if talk is not None:
+        assert talk.shape == (heads, heads)
+    p = _lib.PagedAttnParams()
+    p.q, p.pool, p.out = _p(q), _p(pool), _p(out)
+    p.page_tables, p.tiles = _i32(page_tables, "page_tables"), _i32(tiles, "tiles")
+    p.talk, p.sink = _f32(talk, "talk"), _f32(sink, "sink")
+    p.pool_dtype, p.out_dtype = _dt(pool, "pool"), _dt(out, "out")
+    p.ntiles, p.pt_stride = tiles.shape[0], page_tables.stride(0)
+    p.H, p.G, p.dim, p.vdim, p.page, p.scale = heads, kv_heads, dim, vdim, page, scale
+    p.max_rows = max_rows
+    p.nsplit = max(1, int(nsplit)) if max_rows == 1 else 1
+    partial = None
+    if p.nsplit > 1:
+        partial = torch.empty(q.shape[0] * p.nsplit * heads * (vdim + 2), dtype=torch.float32, device=q.device)
+        p.partial = partial.data_ptr()
+    check(_lib.load().vila_paged_attention(C.byref(p), _stream()), "vila_paged_attention")
+    return out
+
+
+def moe_route_sigmoid(x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], top: int,
+                      groups: int = 1, keep: int = 1):
+    """Sigmoid router with group-limited choice -> (idx int32 [rows, top], weight fp32 [rows, top]):
+    choice = sigmoid(w_router x) + correction, restricted to the `keep` groups (of `groups`) with the largest
+    sum of their two best choice values; weights are the plain sigmoid scores of the chosen experts."""
+    assert x.dim() == 2 and x.stride(1) == 1
+    rows, cols = x.shape
+    E = w_router.shape[0]
+    idx = torch.empty(rows, top, dtype=torch.int32, device=x.device)
+    wt = torch.empty(rows, top, dtype=torch.float32, device=x.device)
+    check(_lib.load().vila_moe_route_sigmoid(_p(x), _dt(x, "x"), x.stride(0), _f32(w_router, "w_router"),
+                                             _f32(correction, "correction"), _p(idx), _p(wt), rows, cols, E, top,
+                                             groups, keep, _stream()), "vila_moe_route_sigmoid")
+    return idx, wt
+
+
+def residual_add_rows(x: torch.Tensor, a: Optional[torch.Tensor] = None, part: Optional[torch.Tensor] = None, *,
+                      n_partials: int = 1, mult: float = 1.0) -> None:
+    """x fp32 [rows, cols] (in place) += mult * (a[r] + sum_j part[r * n_partials + j])"""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    rows, cols = x.shape
+    if a is not None:
+        assert a.shape == (rows, cols) and a.stride(1) == 1
+    if part is not None:
+        assert part.shape == (rows * n_partials, cols) and part.stride(1) == 1
+    check(_lib.load().vila_residual_add_rows(
+        _p(x), _p(a), _dt(a, "a") if a is not None else 0, a.stride(0) if a is not None else 0,
+        _p(part), _dt(part, "part") if part is not None else 0, part.stride(0) if part is not None else 0,
+        n_partials, mult, rows, cols, _stream()), "vila_residual_add_rows")
+
+
+def gelu_mul_gather(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, *, out_dtype=None) -> torch.Tensor:
+    """gelu_tanh(z fp32 [T, n]) * table[ids, col0 : col0 + n]"""
+    assert z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2
+    assert table.dim() == 2 and table.stride(1) == 1 and col0 + z.shape[1] <= table.shape[1]
+    out = torch.empty(z.shape, dtype=out_dtype or z.dtype, device=z.device)
+    check(_lib.load().vila_gelu_mul_gather(_p(z), _p(table), _dt(table, "table"), table.stride(0), _i32(ids, "ids"),
+                                           col0, _p(out), _dt(out, "out"), z.shape[0], z.shape[1], _stream()),
+          "vila_gelu_mul_gather")
     return out

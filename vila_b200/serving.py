@@ -259,11 +259,14 @@ class RaggedBatch:
     """Device-side description of one step.  Row t of the batch is token ids[t]; rows of one sequence
     are consecutive.  seqs [n, 4] = (first row, rows, position of the first row, slot) per sequence;
     tiles = the multi-row sequences cut into <= 16-row pieces, decode_tiles = the single-row ones
-    (same 4 columns); cache_rows[t] = pool row of token t in the paged caches."""
+    (same 4 columns); cache_rows[t] = pool row of token t in the paged caches; positions[t] = position of
+    token t in its sequence; prev_ids[t] = the token before it in its sequence (-1: none; the last token
+    of the previous step for a row that starts a portion); row_seq[t] = index of its sequence in seqs."""
 
-
-    def __init__(self, ids, cache_rows, seqs, tiles, decode_tiles, ctx_rows=None, kv_tiles=None):
+    def __init__(self, ids, cache_rows, seqs, tiles, decode_tiles, ctx_rows=None, kv_tiles=None,
+                 positions=None, prev_ids=None, row_seq=None):
         self.ids, self.cache_rows, self.seqs = ids, cache_rows, seqs
+        self.positions, self.prev_ids, self.row_seq = positions, prev_ids, row_seq
         self.tiles, self.decode_tiles = tiles, decode_tiles
         # un-folded attention for prompt portions that are a large part of their context: ctx_rows = pool
         # rows of ALL positions of those sequences, kv_tiles = their tiles as (row0, rows, pos0, first row
@@ -273,9 +276,11 @@ class RaggedBatch:
 
 
 class HybridCache:
-    """Per-sequence memory of a hybrid model: for every layer that owns a latent, a paged pool
-    [pages * page, width]; for every recurrent layer a state pool [slots, heads, dim, vdim] fp32; one
-    page-table row per slot.  The geometry comes from the model (latent_widths / state_shapes)."""
+    """Per-sequence memory of a model: paged pools [pages * page, width] of per-token rows (a latent per
+    layer that owns one, or k | v rows per attention layer run), state pools [slots, *shape] fp32 of
+    fixed-size per-sequence state (a recurrent matrix, the last inputs of a short convolution), one
+    page-table row per slot.  The geometry comes from the model: latent_widths() / state_shapes() map a key
+    of the model's choosing (a layer index, a (layer, pass) pair) to a row width / a state shape."""
 
     def __init__(self, model, max_tokens: int, slots: int, page: int = LATENT_PAGE):
         dev = model.device
@@ -295,10 +300,11 @@ class HybridCache:
 
 
 class _Sequence:
-    __slots__ = ("slot", "pages", "length")
+    __slots__ = ("slot", "pages", "length", "last_token")
 
     def __init__(self, slot: int):
         self.slot, self.pages, self.length = slot, [], 0
+        self.last_token = -1   # the token before the next one to come (-1: the sequence is empty)
 
 
 class TokenEngine:
@@ -315,7 +321,7 @@ class TokenEngine:
         # the first time it occurs, captured the second time, replayed from then on
         # prompt portions whose rows x unfold_ratio reach the context they attend to are served by expanding
         # keys / values once per step (4x fewer attention flops at kv_rank = 4 x head size); 0: never
-        self.unfold_ratio = 4
+        self.unfold_ratio = 4 if getattr(model, "unfolds_attention", False) else 0
         self.graphs = graphs
         self._decode_graphs: Dict[int, tuple] = {}
         self._decode_seen: Dict[int, int] = {}
@@ -353,6 +359,7 @@ class TokenEngine:
     def _build(self, entries):
         c, dev = self.cache, self.model.device
         ids, rows, seqs, tiles, dec, want_rows = [], [], [], [], [], []
+        poss, prevs, rseq = [], [], []
         ctx, kv_tiles, ctx_at = [], [], 0
         dirty, at = False, 0
         for seq_id, tokens, want in entries:
@@ -365,16 +372,22 @@ class TokenEngine:
             pages = np.asarray(s.pages, dtype=np.int64)
             rows.append(pages[pos // c.page] * c.page + pos % c.page)
             ids.append(np.asarray(tokens, dtype=np.int64))
+            poss.append(pos)
+            prevs.append(np.concatenate(([s.last_token], ids[-1][:-1])))
+            rseq.append(np.full(n, len(seqs)))
+            s.last_token = int(tokens[-1])
             seqs.append((at, n, s.length, s.slot))
             if n == 1:
                 dec.append((at, 1, s.length, s.slot))
             else:
                 for o in range(0, n, TILE_ROWS):
                     tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, s.slot))
-                    kv_tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, ctx_at))
-                allpos = np.arange(0, s.length + n)
-                ctx.append(pages[allpos // c.page] * c.page + allpos % c.page)
-                ctx_at += s.length + n
+                    if self.unfold_ratio > 0:
+                        kv_tiles.append((at + o, min(TILE_ROWS, n - o), s.length + o, ctx_at))
+                if self.unfold_ratio > 0:
+                    allpos = np.arange(0, s.length + n)
+                    ctx.append(pages[allpos // c.page] * c.page + allpos % c.page)
+                    ctx_at += s.length + n
             want_rows.extend(at + int(k) for k in want)
             s.length += n
             at += n
@@ -389,7 +402,8 @@ class TokenEngine:
         # one host->device copy for all index arrays of the step
         parts = [np.concatenate(ids), np.concatenate(rows), np.asarray(seqs).reshape(-1),
                  np.asarray(tiles).reshape(-1), np.asarray(dec).reshape(-1),
-                 np.concatenate(ctx) if ctx else np.zeros(0), np.asarray(kv_tiles).reshape(-1)]
+                 np.concatenate(ctx) if ctx else np.zeros(0), np.asarray(kv_tiles).reshape(-1),
+                 np.concatenate(poss), np.concatenate(prevs), np.concatenate(rseq)]
         flat = torch.from_numpy(np.concatenate(parts).astype(np.int32))
         return flat, [p.size for p in parts], want_rows
 
@@ -399,7 +413,7 @@ class TokenEngine:
         v = [flat[cuts[i]:cuts[i + 1]] for i in range(len(sizes))]
         return RaggedBatch(v[0], v[1], v[2].view(-1, 4), v[3].view(-1, 4) if sizes[3] else None,
                            v[4].view(-1, 4) if sizes[4] else None, v[5] if sizes[5] else None,
-                           v[6].view(-1, 4) if sizes[6] else None)
+                           v[6].view(-1, 4) if sizes[6] else None, v[7], v[8], v[9])
 
     def _decode_step_graphed(self, flat, sizes) -> Tuple[torch.Tensor, torch.Tensor]:
         """All rows are single decoded tokens: replay (or capture) the graph of this row count.
