@@ -1153,6 +1153,208 @@ def run_hybrid_lm(args):
     print(json.dumps(res))
 
 
+# ------------------------------------------------------------------------------------------------
+# --workload parallel_lm: the Lufatar parallel-sublayer language model next to Moronex (the closest
+# model of the package: same engine, fp32 residual, routed experts, sink softmax) at equal width /
+# depth / heads / vocabulary / experts, random weights, bf16
+# ------------------------------------------------------------------------------------------------
+PARALLEL_SIZES = {
+    "w1024": dict(width=1024, vocab=32768, heads=8, kv_heads=2, experts=16, top=2, expert_ff=512, side=64,
+                  kv_rank=512, q_rank=384),
+    "w2048": dict(width=2048, vocab=32768, heads=16, kv_heads=4, experts=32, top=4, expert_ff=704, side=128,
+                  kv_rank=512, q_rank=768),
+    "w4096": dict(width=4096, vocab=32768, heads=32, kv_heads=8, experts=64, top=6, expert_ff=1408, side=128,
+                  kv_rank=512, q_rank=1536),
+}
+
+
+def parallel_lm_config(z):
+    mix = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=128, vdim=128, rot={"base": 10000.0, "dims": 64},
+               scale=128 ** -0.5)
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": 4, "keep": 2}}}
+    layers = [{"type": "attention", "mixer": dict(mix), "mlp": dict(moe)} for _ in range(4)]
+    return {"architecture": "Lufatar", "canon": {"taps": 4},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7919}},
+            "layers": layers, "loop": {"start": 1, "stop": 3, "times": 1}, "norm": {"eps": 1e-5, "groups": 4},
+            "residual_mult": 0.5, "token_side": {"dim": z["side"]}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def parallel_lm_twin(z):
+    """Moronex with the same width / heads / vocabulary / experts: 4 latent-attention layers with routed experts"""
+    lat = dict(heads=z["heads"], dim=128, vdim=128, kv_rank=z["kv_rank"], q_rank=z["q_rank"], scale=128 ** -0.5)
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}}
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": dict(moe)} for _ in range(4)]
+    return {"architecture": "Moronex", "layers": layers, "norm": {"eps": 1e-5}, "vocab": z["vocab"], "width": z["width"]}
+
+
+def parallel_lm_block(args, peaks):
+    import torch
+
+    from vila_b200 import ops
+    from vila_b200.model import LufatarConfig, LufatarForCausalLM, MoronexConfig, MoronexForCausalLM
+    from vila_b200.serving import TokenEngine
+    dev = torch.device("cuda:0")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def timed(fn, reps=args.steps, warm=max(3, args.warmup), setup=None):
+        ts = []
+        for i in range(warm + reps):
+            if setup is not None:
+                setup()
+            flush.fill_(i & 255)     # evict L2 (126 MB) between iterations
+            a, b = ev(), ev()
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            if i >= warm:
+                ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    S, B, CTX, NEW = 2048, 8, 1024, 32
+    tf, gbs = peaks["bf16_tflops"], peaks["hbm_gbs"]
+    bf = torch.bfloat16
+    out = {}
+    t00 = time.time()
+
+    def log(msg):
+        print("[parallel_lm %6.1fs] %s" % (time.time() - t00, msg), file=sys.stderr, flush=True)
+
+    def engine_numbers(lm, prompt):
+        eng = TokenEngine(lm, max_tokens=B * (CTX + 4 * NEW + 64), slots=B)
+        t_pre = timed(lambda: eng.step([("p", prompt, [S - 1])]), setup=lambda: eng.release("p"))
+        eng.release("p")
+        for b in range(B):
+            eng.step([(b, prompt[:CTX], [])])
+        step_in = [[(b, [int(prompt[(k * 7 + b) % S])], [0]) for b in range(B)] for k in range(NEW)]
+
+        def decode_run():
+            for k in range(NEW):
+                eng.step(step_in[k])
+        t_dec = timed(decode_run, reps=3, warm=1)     # contexts grow CTX .. CTX + 4 * NEW: fits the reserve
+        for b in range(B):
+            eng.release(b)
+        n = sum(v.numel() for v in lm.weights.values())
+        return eng, {"params_m": n / 1e6, "prefill_tok_s": S / t_pre * 1e3, "prefill_ms": t_pre,
+                     "decode_tok_s": B * NEW / t_dec * 1e3, "decode_ms_per_step": t_dec / NEW}
+
+    for name, z in PARALLEL_SIZES.items():
+        if args.sizes and name not in args.sizes.split(","):
+            continue
+        W, H, G, R = z["width"], z["heads"], z["kv_heads"], z["kv_rank"]
+        g = torch.Generator().manual_seed(0)
+        prompt = torch.randint(0, z["vocab"], (S,), generator=g).tolist()
+        log("size %s: lufatar" % name)
+        lm = LufatarForCausalLM(LufatarConfig.from_dict(parallel_lm_config(z)), dev, bf).init_random(0, on_device=True)
+        eng, res_new = engine_numbers(lm, prompt)
+        log("size %s: moronex" % name)
+        tw = MoronexForCausalLM(MoronexConfig.from_dict(parallel_lm_twin(z)), dev, bf).init_random(0, on_device=True)
+        eng2, res_old = engine_numbers(tw, prompt)
+        # ---- kernel beside the like kernel ---------------------------------------------------------------
+        log("kernel ledger")
+        led = {}
+        L0, M0 = lm.layers[0], tw.layers[0]
+        page = eng.cache.page
+        npg = eng.cache.n_pages
+        pool = eng.cache.latent[0]
+        pt = torch.arange(npg, dtype=torch.int32, device=dev).view(1, -1).repeat(B, 1).contiguous()
+        tiles = torch.tensor([(o, 16, o, 0) for o in range(0, S, 16)], dtype=torch.int32, device=dev)
+        q = torch.randn(S, H * 128, device=dev)
+        akw = dict(heads=H, kv_heads=G, dim=128, vdim=128, page=page, scale=0.088, talk=L0.talk, sink=L0.sink)
+        t = timed(lambda: ops.paged_attention(q, pool, pt, tiles, max_rows=16, **akw))
+        fl = H * (S * (S + 1) / 2) * 4 * 128
+        led["paged_attention prefill (head mixing, fp32 scores and weights, CUDA cores)"] = {
+            "ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        kvb = torch.randn(S, H * 256, device=dev).to(bf)
+        qb = torch.randn(S, H * 128, device=dev).to(bf)
+        gate = torch.randn(S, H, device=dev).to(bf)
+        t = timed(lambda: ops.sink_attention(qb, kvb[:, :H * 128], kvb[:, H * 128:], tiles, heads=H, scale=0.088,
+                                             sink=M0.sink, gate=gate))
+        led["moronex sink_attention prefill (un-folded, fp32 scores and weights, CUDA cores)"] = {
+            "ms": t, "tflops": fl / t / 1e9, "of_bf16_peak": fl / t / 1e9 / tf}
+        dt_ = torch.tensor([(b, 1, CTX - 1, b) for b in range(B)], dtype=torch.int32, device=dev)
+        pt2 = ((torch.arange(B, device=dev, dtype=torch.int32)[:, None] * (CTX // page) +
+                torch.arange(npg, device=dev, dtype=torch.int32)[None]) % npg).contiguous()
+        t = timed(lambda: ops.paged_attention(q[:B], pool, pt2, dt_, max_rows=1, nsplit=eng.cache.decode_splits, **akw))
+        by = B * CTX * G * 256 * 2
+        led["paged_attention decode (8 x 1024 tokens)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        qa = torch.randn(B, H * R, device=dev)
+        pool2 = eng2.cache.latent[0]
+        t = timed(lambda: ops.latent_attention(qa, pool2, pt2, dt_, heads=H, page=page, scale=0.088, sink=M0.sink,
+                                               gate=gate[:B], decode=True, nsplit=eng2.cache.decode_splits))
+        by2 = B * CTX * R * 2
+        led["moronex latent_attention decode (8 x 1024 tokens)"] = {"ms": t, "gbs": by2 / t / 1e6, "of_hbm": by2 / t / 1e6 / gbs}
+        h = torch.randn(S, W, device=dev).to(bf)
+        fl_new = 2 * 3 * S * z["top"] * z["expert_ff"] * W
+        fl_old = 2 * 2 * S * z["top"] * z["expert_ff"] * W
+        t = timed(lambda: lm._experts(L0, h))
+        led["routed experts prefill: sigmoid group router + group + 2 grouped GEMMs (gate|up, down)"] = {
+            "ms": t, "tflops": fl_new / t / 1e9, "of_bf16_peak": fl_new / t / 1e9 / tf}
+        t = timed(lambda: tw._experts(M0, h))
+        led["moronex routed experts prefill: softmax router + group + 2 grouped GEMMs (up, down)"] = {
+            "ms": t, "tflops": fl_old / t / 1e9, "of_bf16_peak": fl_old / t / 1e9 / tf}
+        t = timed(lambda: lm._experts(L0, h[:B]))
+        by = 3 * min(z["experts"], B * z["top"]) * z["expert_ff"] * W * 2
+        led["routed experts decode (8 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        t = timed(lambda: tw._experts(M0, h[:B]))
+        by = 2 * min(z["experts"], B * z["top"]) * z["expert_ff"] * W * 2
+        led["moronex routed experts decode (8 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        x = torch.randn(S, W, device=dev)
+        ar = torch.arange(S, dtype=torch.int32, device=dev)
+        sq = torch.tensor([[0, S, 0, 0]], dtype=torch.int32, device=dev)
+        rs = torch.zeros(S, dtype=torch.int32, device=dev)
+        batch = type("B", (), dict(seqs=sq, row_seq=rs))
+        st = eng.cache.state[(0, 0)]
+        t = timed(lambda: lm._sublayer_input(x, L0.norm1, L0.canon1, st, batch))
+        by = S * W * (4 + 2)
+        led["sublayer input: group norm + short convolution + state (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        t = timed(lambda: ops.rmsnorm_rows(x, M0.norm1, 1e-5, w_offset=1.0, out_dtype=bf))
+        led["moronex rmsnorm_rows (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        qkv = torch.randn(S, (H + 2 * G) * 128, device=dev).to(bf)
+        t = timed(lambda: ops.rope_append(qkv, ar, ar, pool, heads=H, kv_heads=G, dim=128, vdim=128, inv_freq=L0.inv_freq,
+                                          unit_norm=True, eps=1e-5))
+        by = S * ((H + 2 * G) * 128 * 2 + H * 128 * 4 + 2 * G * 128 * 2)
+        led["rope_append: rotary + unit norm + K|V append (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        y = torch.randn(S, W, device=dev).to(bf)
+        parts = torch.randn(S * z["top"], W, device=dev)
+        t = timed(lambda: ops.residual_add_rows(x, y, parts, n_partials=z["top"], mult=0.5))
+        by = S * W * (8 + 2 + 4 * z["top"])
+        led["residual_add_rows: x += m (attention + sum of expert partials) (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        gt = torch.randn(S, W, device=dev).to(bf)
+        t = timed(lambda: ops.gated_norm_residual(x, parts, n_partials=z["top"], gate=gt, gate_bias=M0.rg2_b, w=M0.norm2b, w_offset=1.0, eps=1e-5))
+        by = S * W * (8 + 2 + 4 * z["top"])
+        led["moronex gated_norm_residual with expert partials (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        t = timed(lambda: lm._token_side(L0, x, type("B", (), dict(ids=ar))))
+        led["token side input: gate GEMM + gelu x table + proj GEMM + normed update (2048 rows)"] = {"ms": t}
+        out[name] = {"lufatar": res_new, "moronex": res_old, "kernels": led}
+        del lm, tw, eng, eng2
+        torch.cuda.empty_cache()
+    return {"workload": "parallel_lm: 4 Lufatar layers (rotary GQA with head mixing + routed clamped-GLU experts in "
+                        "parallel, short convolutions, token side input) vs 4 Moronex layers (latent attention + routed "
+                        "experts) of equal width / heads / vocabulary / experts; prefill: one %d-token prompt; decode: %d "
+                        "sequences x %d-token context, %d steps" % (S, B, CTX, NEW),
+            "dtype": "bf16", "data": "synthetic (random weights, random ids)",
+            "l2_policy": "256 MB buffer written between timed iterations", "peaks": peaks, "sizes": out}
+
+
+def run_parallel_lm(args):
+    import torch
+    assert torch.cuda.is_available(), "bench.py --workload parallel_lm needs a GPU"
+    import faulthandler
+    faulthandler.dump_traceback_later(int(os.environ.get("VILA_BENCH_WATCHDOG_S", "480")), exit=True)
+    peaks = read_peaks()
+    with ClockSampler(0) as cs:
+        res = parallel_lm_block(args, peaks)
+    res["clocks"] = cs.summary()
+    from vila_b200 import _lib
+    res["gpu_launches"] = _lib.LAUNCHES
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1167,12 +1369,16 @@ def main():
     ap.add_argument("--sp-steps", type=int, default=10)
     ap.add_argument("--profile", action="store_true",
                     help="profiling aid (ncu): 1 warm-up, 8 new tokens, no extra blocks; NOT a valid bench number")
-    ap.add_argument("--sizes", default="", help="hybrid_lm: comma-separated subset of " + ",".join(HYBRID_SIZES))
-    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm"],
-                    help="headline (default): the NVILA-8B serving step; hybrid_lm: Moronex vs Qwen2 at equal size")
+    ap.add_argument("--sizes", default="", help="hybrid_lm / parallel_lm: comma-separated subset of the workload's sizes ("
+                    + ",".join(HYBRID_SIZES) + " / " + ",".join(PARALLEL_SIZES) + ")")
+    ap.add_argument("--workload", default="headline", choices=["headline", "hybrid_lm", "parallel_lm"],
+                    help="headline (default): the NVILA-8B serving step; hybrid_lm: Moronex vs Qwen2 at equal size; "
+                         "parallel_lm: Lufatar vs Moronex at equal size")
     args = ap.parse_args()
     if args.workload == "hybrid_lm":
         return run_hybrid_lm(args)
+    if args.workload == "parallel_lm":
+        return run_parallel_lm(args)
     if args.profile:
         global NEW_TOKENS
         NEW_TOKENS = 8

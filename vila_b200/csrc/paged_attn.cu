@@ -87,6 +87,69 @@ __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
   return static_cast<size_t>(pt[j / page]) * page + (j % page);
 }
 
+// K | V rows of a key block, widened to fp32: one warp per key.  16-byte loads when the head sizes allow
+// (bf16: multiples of 8, fp32: multiples of 4; the pool row is then 16-byte aligned as well).
+__device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_paged_attn_params& p,
+                                              const int32_t* pt, int j0, int nkeys, int BK, int D4, int DS, int V4) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.G, D = p.dim, V = p.vdim;
+  const size_t prw = static_cast<size_t>(G) * (D + V);
+  const bool vec16 = p.pool_dtype == VILA_DT_BF16 && (D & 7) == 0 && (V & 7) == 0;
+  const bool vec32 = p.pool_dtype == VILA_DT_F32 && (D & 3) == 0 && (V & 3) == 0;
+  for (int jj = warp; jj < BK; jj += kWarps) {
+    const int j = j0 + jj;
+    float* kd = Ks + jj * G * DS;
+    float* vd = Vs + jj * G * V4;
+    if (j >= nkeys) {
+      for (int x = lane; x < G * DS; x += 32) kd[x] = 0.f;
+      for (int x = lane; x < G * V4; x += 32) vd[x] = 0.f;
+      continue;
+    }
+    const size_t src = pool_row(pt, p.page, j) * prw;
+    if (vec16) {
+      const __nv_bfloat16* base = static_cast<const __nv_bfloat16*>(p.pool) + src;
+      const uint4* k4 = reinterpret_cast<const uint4*>(base);
+      const uint4* v4 = reinterpret_cast<const uint4*>(base + static_cast<size_t>(G) * D);
+      for (int x = lane; x < (G * D) >> 3; x += 32) {
+        const uint4 u = __ldg(k4 + x);
+        const int e = x << 3, g = e / D, k = e - g * D;
+        float* d = kd + g * DS + k;
+        *reinterpret_cast<float4*>(d) = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                                                    __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+        *reinterpret_cast<float4*>(d + 4) = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u),
+                                                        __uint_as_float(u.w << 16), __uint_as_float(u.w & 0xffff0000u));
+      }
+      for (int x = lane; x < (G * V) >> 3; x += 32) {
+        const uint4 u = __ldg(v4 + x);
+        float* d = vd + (x << 3);
+        *reinterpret_cast<float4*>(d) = make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                                                    __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+        *reinterpret_cast<float4*>(d + 4) = make_float4(__uint_as_float(u.z << 16), __uint_as_float(u.z & 0xffff0000u),
+                                                        __uint_as_float(u.w << 16), __uint_as_float(u.w & 0xffff0000u));
+      }
+    } else if (vec32) {
+      const float* base = static_cast<const float*>(p.pool) + src;
+      const float4* k4 = reinterpret_cast<const float4*>(base);
+      const float4* v4 = reinterpret_cast<const float4*>(base + static_cast<size_t>(G) * D);
+      for (int x = lane; x < (G * D) >> 2; x += 32) {
+        const int e = x << 2, g = e / D, k = e - g * D;
+        *reinterpret_cast<float4*>(kd + g * DS + k) = __ldg(k4 + x);
+      }
+      for (int x = lane; x < (G * V) >> 2; x += 32) *reinterpret_cast<float4*>(vd + (x << 2)) = __ldg(v4 + x);
+    } else {
+      for (int x = lane; x < G * D4; x += 32) {
+        const int g = x / D4, k = x - g * D4;
+        kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + static_cast<size_t>(g) * D + k) : 0.f;
+      }
+      const size_t vsrc = src + static_cast<size_t>(G) * D;
+      for (int x = lane; x < G * V4; x += 32) {
+        const int g = x / V4, k = x - g * V4;
+        vd[x] = k < V ? ld_any(p.pool, p.pool_dtype, vsrc + static_cast<size_t>(g) * V + k) : 0.f;
+      }
+    }
+  }
+}
+
 // Shared memory (floats):  Qs [BQ * H][D4] (scale folded in) | Ks [BK][G][DS] | Vs [BK][G][V4] |
 //   Ss [BQ * H][BK] raw scores | Ps [BQ * H][BK] weights | talk [H * H] | m, l, alpha [BQ * H]
 // DS = D4 + 4: consecutive keys start 4 banks apart, so the float4 reads of 8 keys do not collide.
@@ -135,27 +198,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
   for (int b = split; b < nblocks; b += nsplit) {
     const int j0 = b * BK;
     __syncthreads();
-    // K | V rows of the block, widened to fp32; one warp per key
-    for (int jj = warp; jj < BK; jj += kWarps) {
-      const int j = j0 + jj;
-      float* kd = Ks + jj * G * DS;
-      float* vd = Vs + jj * G * V4;
-      if (j >= nkeys) {
-        for (int x = lane; x < G * DS; x += 32) kd[x] = 0.f;
-        for (int x = lane; x < G * V4; x += 32) vd[x] = 0.f;
-        continue;
-      }
-      const size_t src = pool_row(pt, p.page, j) * prw;
-      for (int x = lane; x < G * D4; x += 32) {
-        const int g = x / D4, k = x - g * D4;
-        kd[g * DS + k] = k < D ? ld_any(p.pool, p.pool_dtype, src + static_cast<size_t>(g) * D + k) : 0.f;
-      }
-      const size_t vsrc = src + static_cast<size_t>(G) * D;
-      for (int x = lane; x < G * V4; x += 32) {
-        const int g = x / V4, k = x - g * V4;
-        vd[x] = k < V ? ld_any(p.pool, p.pool_dtype, vsrc + static_cast<size_t>(g) * V + k) : 0.f;
-      }
-    }
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4);
     __syncthreads();
     // raw scores of every (score row, key)
     for (int idx = tid; idx < R * BK; idx += kThreads) {
@@ -239,6 +282,159 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
   }
 }
 
+// Prompt portions: BQ (a multiple of 4) rows x all heads per CTA, register-tiled.  Score rows are ordered
+// head-major (r = h * BQ + i) so that 4 consecutive score rows are 4 query rows of ONE head: they share
+// the key / value head, and a thread that owns such a block of 4 keeps
+//   scores:        4 rows x 2 keys (keys jp and jp + BK / 2) per thread, q and k as float4 pieces: 6 shared
+//                  loads per 32 multiply-adds
+//   weighted sum:  4 rows x 4 value columns per accumulator, the 4 weights of a key as ONE float4
+//                  (Ps is [row block][key][4]): 2 shared loads per 16 multiply-adds
+// Shared memory (floats): Qs [R][D4] | Ks [BK][G][DS] | Vs [BK][G][V4] | Ss [R][BK] | Ps [R / 4][BK][4] |
+//   m, l, alpha [R] | talk [H * H]
+template <int NACC>
+__global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_paged_attn_params p, const AttnShape sh) {
+  extern __shared__ __align__(16) float sm[];
+  const int H = p.H, G = p.G, D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK, HK = sh.BK >> 1;
+  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, NB = R >> 2, rep = H / G;
+  float* Qs = sm;
+  float* Ks = Qs + R * D4;
+  float* Vs = Ks + BK * G * DS;
+  float* Ss = Vs + BK * G * V4;
+  float* Ps = Ss + R * BK;
+  float* m_s = Ps + R * BK;
+  float* l_s = m_s + R;
+  float* a_s = l_s + R;
+  float* Tk = a_s + R;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int* tile = p.tiles + 4 * blockIdx.x;
+  const int i0 = blockIdx.y * BQ;
+  const int n_tile = tile[1];
+  if (i0 >= n_tile) return;
+  const int row0 = tile[0] + i0, n = min(BQ, n_tile - i0), pos0 = tile[2] + i0;
+  const int32_t* pt = p.page_tables + static_cast<size_t>(tile[3]) * p.pt_stride;
+
+  for (int idx = tid; idx < R * D4; idx += kThreads) {
+    const int r = idx / D4, k = idx - r * D4, h = r / BQ, i = r - h * BQ;
+    Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * p.scale : 0.f;
+  }
+  for (int idx = tid; idx < H * H; idx += kThreads) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
+  for (int r = tid; r < R; r += kThreads) {
+    m_s[r] = p.sink ? p.sink[r / BQ] : kNegBig;
+    l_s[r] = p.sink ? 1.0f : 0.0f;
+  }
+  float4 acc[NACC][4];
+#pragma unroll
+  for (int a = 0; a < NACC; ++a)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[a][k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  const int vq = V4 >> 2;
+  const int nout = NB * vq;               // accumulator items of the CTA: o -> (row block, float4 column)
+  const int nkeys = pos0 + n;
+  const int d4n = D4 >> 2;
+
+  for (int j0 = 0; j0 < nkeys; j0 += BK) {
+    __syncthreads();
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4);
+    __syncthreads();
+    for (int item = tid; item < NB * HK; item += kThreads) {
+      const int rb = item / HK, jp = item - rb * HK;
+      const int g = ((rb << 2) / BQ) / rep;
+      const float4* q0 = reinterpret_cast<const float4*>(Qs + (rb << 2) * D4);
+      const float4* k0 = reinterpret_cast<const float4*>(Ks + (jp * G + g) * DS);
+      const float4* k1 = reinterpret_cast<const float4*>(Ks + ((jp + HK) * G + g) * DS);
+      float s[4][2];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) s[a][0] = s[a][1] = 0.f;
+#pragma unroll 2
+      for (int k = 0; k < d4n; ++k) {
+        const float4 ka = k0[k], kb = k1[k];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float4 qv = q0[a * d4n + k];
+          s[a][0] = fmaf(qv.x, ka.x, s[a][0]); s[a][0] = fmaf(qv.y, ka.y, s[a][0]);
+          s[a][0] = fmaf(qv.z, ka.z, s[a][0]); s[a][0] = fmaf(qv.w, ka.w, s[a][0]);
+          s[a][1] = fmaf(qv.x, kb.x, s[a][1]); s[a][1] = fmaf(qv.y, kb.y, s[a][1]);
+          s[a][1] = fmaf(qv.z, kb.z, s[a][1]); s[a][1] = fmaf(qv.w, kb.w, s[a][1]);
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        Ss[((rb << 2) + a) * BK + jp] = s[a][0];
+        Ss[((rb << 2) + a) * BK + jp + HK] = s[a][1];
+      }
+    }
+    __syncthreads();
+    for (int r = warp; r < R; r += kWarps) {
+      const int h = r / BQ, i = r - h * BQ;
+      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i;
+      float s = 0.f;
+      if (lane < BK) {
+        const float* tk = Tk + h * H;
+        const float* sr = Ss + i * BK + lane;
+        for (int g = 0; g < H; ++g) s = fmaf(tk[g], sr[g * BQ * BK], s);
+      }
+      s = valid ? s : kNegBig;
+      const float m_old = m_s[r];
+      const float m_new = fmaxf(m_old, warp_max(s));
+      const float pj = valid ? expf(s - m_new) : 0.f;
+      const float ps = warp_sum(pj);
+      if (lane < BK) Ps[(((r >> 2) * BK + lane) << 2) + (r & 3)] = pj;
+      if (lane == 0) {
+        const float alpha = expf(m_old - m_new);
+        a_s[r] = alpha;
+        l_s[r] = l_s[r] * alpha + ps;
+        m_s[r] = m_new;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int a = 0; a < NACC; ++a) {
+      const int o = tid + a * kThreads;
+      if (o < nout) {
+        const int rb = o / vq, c4 = o - rb * vq;
+        const int g = ((rb << 2) / BQ) / rep;
+        const float4 al = *reinterpret_cast<const float4*>(a_s + (rb << 2));
+        const float alv[4] = {al.x, al.y, al.z, al.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          acc[a][k].x *= alv[k]; acc[a][k].y *= alv[k]; acc[a][k].z *= alv[k]; acc[a][k].w *= alv[k];
+        }
+        const float4* pr = reinterpret_cast<const float4*>(Ps + ((rb * BK) << 2));
+        const float* vr = Vs + g * V4 + 4 * c4;
+#pragma unroll 4
+        for (int jj = 0; jj < BK; ++jj) {
+          const float4 pw = pr[jj];
+          const float4 c = *reinterpret_cast<const float4*>(vr + jj * G * V4);
+          const float pv[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            acc[a][k].x = fmaf(pv[k], c.x, acc[a][k].x); acc[a][k].y = fmaf(pv[k], c.y, acc[a][k].y);
+            acc[a][k].z = fmaf(pv[k], c.z, acc[a][k].z); acc[a][k].w = fmaf(pv[k], c.w, acc[a][k].w);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int a = 0; a < NACC; ++a) {
+    const int o = tid + a * kThreads;
+    if (o >= nout) continue;
+    const int rb = o / vq, c4 = o - rb * vq;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int r = (rb << 2) + k, h = r / BQ, i = r - h * BQ;
+      if (i >= n) continue;
+      const float inv = 1.0f / l_s[r];
+      const float v[4] = {acc[a][k].x, acc[a][k].y, acc[a][k].z, acc[a][k].w};
+      const size_t ob = (static_cast<size_t>(row0 + i) * H + h) * V + 4 * c4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (4 * c4 + e < V) st_any(p.out, p.out_dtype, ob + e, v[e] * inv);
+    }
+  }
+}
+
 // one CTA per (decoded row, head): combine the nsplit partial triples in split order
 __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_attn_params p) {
   const int* tile = p.tiles + 4 * blockIdx.x;
@@ -279,11 +475,36 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
   VB_CHECK(p.H >= 1 && p.G >= 1 && p.H % p.G == 0 && p.dim >= 1 && p.vdim >= 1 && p.page >= 1 && p.nsplit >= 1 &&
                p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
            "paged_attention: H=%d G=%d dim=%d vdim=%d page=%d nsplit=%d", p.H, p.G, p.dim, p.vdim, p.page, p.nsplit);
-  // rows per CTA: about 64 score rows (BQ * H); decoded tokens (nsplit given) are one-row tiles
   constexpr size_t kSmemMax = 200 * 1024;
-  AttnShape sh;
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
+  AttnShape sh;
+  if (p.max_rows > 1 && p.H <= 32) {
+    // prompt portions: the register-tiled kernel, 4 .. 16 rows per CTA (about 64 score rows, 128 at most)
+    sh.BQ = 16;
+    while (sh.BQ > 4 && sh.BQ * p.H > 64) sh.BQ >>= 1;
+    sh.BK = 32;
+    while (attn_smem(p, sh.BQ, sh.BK) > kSmemMax && sh.BK > 8) sh.BK >>= 1;
+    const int nacc4 = ((sh.BQ * p.H / 4) * (round4(p.vdim) >> 2) + kThreads - 1) / kThreads;
+    const size_t smem4 = attn_smem(p, sh.BQ, sh.BK);
+    if (smem4 <= kSmemMax && nacc4 <= 4) {
+      sh.sub = (p.max_rows + sh.BQ - 1) / sh.BQ;
+      const dim3 grid4(p.ntiles, sh.sub, 1);
+#define VB_PAGED4(N)                                                                                             \
+  do {                                                                                                           \
+    if (smem4 > 48 * 1024)                                                                                       \
+      VB_CUDA(cudaFuncSetAttribute(paged_attn_tile4_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                                   static_cast<int>(smem4)));                                                    \
+    VB_CUDA(launch_serial(paged_attn_tile4_kernel<N>, grid4, dim3(kThreads), smem4, stream, p, sh));             \
+  } while (0)
+      if (nacc4 <= 1) VB_PAGED4(1);
+      else if (nacc4 <= 2) VB_PAGED4(2);
+      else VB_PAGED4(4);
+#undef VB_PAGED4
+      return 0;
+    }
+  }
+  // decoded tokens (one-row tiles, keys optionally split over CTAs) and shapes the tiled kernel does not take
   sh.BQ = 1;
   while (sh.BQ < p.max_rows) sh.BQ <<= 1;
   while (sh.BQ > 1 && sh.BQ * p.H > 64) sh.BQ >>= 1;
