@@ -1308,12 +1308,14 @@ def parallel_lm_block(args, peaks):
         sq = torch.tensor([[0, S, 0, 0]], dtype=torch.int32, device=dev)
         rs = torch.zeros(S, dtype=torch.int32, device=dev)
         batch = type("B", (), dict(seqs=sq, row_seq=rs))
-        st = eng.cache.state[(0, 0)]
-        t = timed(lambda: lm._sublayer_input(x, L0.norm1, L0.canon1, st, batch))
+        cache1 = type("C", (), dict(state=eng.cache.state))
+        t = timed(lambda: lm._sublayer_inputs(L0, x, batch, cache1, 0))
         by = S * W * (4 + 2)
-        led["sublayer input: group norm + short convolution + state (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        by = S * W * (4 + 2 * 2)
+        led["sublayer inputs of mixer and experts: group norm + short convolution + state, fused (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
         t = timed(lambda: ops.rmsnorm_rows(x, M0.norm1, 1e-5, w_offset=1.0, out_dtype=bf))
-        led["moronex rmsnorm_rows (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
+        by = S * W * (4 + 2)
+        led["moronex rmsnorm_rows (2048 rows, one sublayer)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
         qkv = torch.randn(S, (H + 2 * G) * 128, device=dev).to(bf)
         t = timed(lambda: ops.rope_append(qkv, ar, ar, pool, heads=H, kv_heads=G, dim=128, vdim=128, inv_freq=L0.inv_freq,
                                           unit_norm=True, eps=1e-5))
@@ -1328,7 +1330,8 @@ def parallel_lm_block(args, peaks):
         t = timed(lambda: ops.gated_norm_residual(x, parts, n_partials=z["top"], gate=gt, gate_bias=M0.rg2_b, w=M0.norm2b, w_offset=1.0, eps=1e-5))
         by = S * W * (8 + 2 + 4 * z["top"])
         led["moronex gated_norm_residual with expert partials (2048 rows)"] = {"ms": t, "gbs": by / t / 1e6, "of_hbm": by / t / 1e6 / gbs}
-        t = timed(lambda: lm._token_side(L0, x, type("B", (), dict(ids=ar))))
+        xcb = x.to(bf)
+        t = timed(lambda: lm._token_side(L0, x, xcb, type("B", (), dict(ids=ar))))
         led["token side input: gate GEMM + gelu x table + proj GEMM + normed update (2048 rows)"] = {"ms": t}
         out[name] = {"lufatar": res_new, "moronex": res_old, "kernels": led}
         del lm, tw, eng, eng2

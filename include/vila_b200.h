@@ -530,10 +530,28 @@ int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float*
                            const float* correction, int32_t* idx, float* weight, int rows, int cols,
                            int experts, int top, int groups, int keep, void* stream);
 
-/* x[r, :] += mult * (a[r, :] + sum_{j < n_partials} part[r * n_partials + j, :])  (a or part may be NULL) */
+/* x[r, :] += mult * (a[r, :] + sum_{j < n_partials} part[r * n_partials + j, :])  (a or part may be NULL);
+ * copy != NULL also receives the updated rows in copy_dtype (the next projection's operand). */
 int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,
-                           int part_dtype, int64_t ldp, int n_partials, float mult, int rows, int cols,
-                           void* stream);
+                           int part_dtype, int64_t ldp, int n_partials, float mult, void* copy,
+                           int copy_dtype, int rows, int cols, void* stream);
+
+/* Group RMS norm + causal short convolution for up to two sublayers that read the same rows x, in one
+ * pass (vila_group_rmsnorm_rows followed by vila_short_conv_rows / vila_short_conv_state per sublayer):
+ *   h_k = groupnorm(x) * (norm_w[k] + w_offset);  out[k] = h_k + conv(h_k, conv_w[k]);  state[k] <- last inputs
+ * The normalisation is shared, weights / taps / state / output are per sublayer (nsub = 1 or 2). */
+typedef struct vila_norm_conv_params {
+  const float* x; /* [rows, cols] contiguous */
+  const float* norm_w[2];
+  const void* conv_w[2]; /* [cols, taps] */
+  float* state[2];       /* [slots, taps - 1, cols] */
+  void* out[2];          /* [rows, cols] */
+  const int32_t* seqs;
+  const int32_t* row_seq;
+  int32_t conv_w_dtype, out_dtype, rows, nseq, cols, groups, taps, nsub;
+  float eps, w_offset;
+} vila_norm_conv_params;
+int vila_norm_conv_rows(const vila_norm_conv_params* p, void* stream);
 
 /* vila_gated_norm_residual with the update multiplied by `mult` */
 int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
@@ -541,9 +559,9 @@ int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, 
                                     int bias_dtype, const void* w, int w_dtype, float w_offset, float eps,
                                     float mult, int rows, int cols, void* stream);
 
-/* out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]   (z fp32 [T, cols]; a per-token side input
- * gated by a projection of the stream) */
-int vila_gelu_mul_gather(const float* z, const void* table, int table_dtype, int64_t ld_table,
+/* out[t, j] = gelu_tanh(z[t, j]) * table[ids[t], col0 + j]   (z [T, cols] contiguous; a per-token side
+ * input gated by a projection of the stream) */
+int vila_gelu_mul_gather(const void* z, int z_dtype, const void* table, int table_dtype, int64_t ld_table,
                          const int32_t* ids, int col0, void* out, int out_dtype, int rows, int cols,
                          void* stream);
 

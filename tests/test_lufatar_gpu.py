@@ -229,6 +229,46 @@ def test_short_conv_in_portions_through_reused_slots(cuda, taps):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
+@pytest.mark.parametrize("taps,groups,nsub", [(1, 1, 2), (3, 3, 1), (4, 2, 2), (6, 1, 2)])
+def test_fused_norm_and_short_conv_in_portions(cuda, dtype, taps, groups, nsub):
+    """group norm + convolution of one or two sublayers in one pass, two sequences in portions of 1, 2, ...
+    rows through stale slots, against norm-then-convolution over the whole sequence"""
+    ops = _ops()
+    C, slots = 48, 3
+    nw = [1 + rnd(C, seed=10 + k, scale=0.2) for k in range(nsub)]
+    cw = [rnd(C, taps, seed=20 + k, scale=0.5).to(dtype) for k in range(nsub)]
+    seqs = {"a": rnd(23, C, seed=4, scale=3.0).float(), "b": rnd(31, C, seed=5, scale=0.2).float()}
+    want = {n: [O.short_conv_residual(O.group_norm(v.double(), nw[k], groups, 1e-5), cw[k].double()) for k in range(nsub)]
+            for n, v in seqs.items()}
+    state = [torch.full((slots, max(taps - 1, 1), C), 55.0, device="cuda")[:, :taps - 1].contiguous() for _ in range(nsub)]
+    slot = {"a": 1, "b": 2}
+    cuts = {"a": [1, 2, 1, 5, 1, 1, 3, 9], "b": [2, 2, 7, 1, 1, 1, 17]}
+    at = {"a": 0, "b": 0}
+    got = {n: [[] for _ in range(nsub)] for n in seqs}
+    for step in range(8):
+        rows, sq, rseq, names = [], [], [], []
+        for name in ("a", "b"):
+            if step < len(cuts[name]):
+                n = cuts[name][step]
+                sq.append((sum(r.shape[0] for r in rows), n, at[name], slot[name]))
+                rseq += [len(sq) - 1] * n
+                rows.append(seqs[name][at[name]:at[name] + n])
+                names.append((name, n))
+                at[name] += n
+        outs = ops.norm_conv_rows(torch.cat(rows).cuda(), [w.float().cuda() for w in nw], [w.cuda() for w in cw],
+                                  state if taps > 1 else [None] * nsub, torch.tensor(sq, dtype=torch.int32).cuda(),
+                                  torch.tensor(rseq, dtype=torch.int32).cuda(), groups=groups, eps=1e-5, out_dtype=F32)
+        o = 0
+        for name, n in names:
+            for k in range(nsub):
+                got[name][k].append(outs[k][o:o + n].cpu())
+            o += n
+    for name in seqs:
+        for k in range(nsub):
+            assert rel(torch.cat(got[name][k]), want[name][k]) < 1e-5, (name, k)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF])
 @pytest.mark.parametrize("H,G,dim,vdim,rot", [(3, 3, 12, 20, 8), (4, 1, 10, 6, 10), (2, 2, 16, 16, 0), (10, 2, 64, 32, 32)])
 def test_rope_append(cuda, dtype, H, G, dim, vdim, rot):
     """positions near 0, at a page border and very far (the phase of a far position needs more than fp32
@@ -468,8 +508,8 @@ def test_small_row_ops(cuda):
     ops.residual_add_rows(x, a.cuda(), parts.float().cuda(), n_partials=3, mult=0.7)
     assert rel(x, x0 + 0.7 * (a.double() + parts.view(9, 3, 20).sum(1))) < 1e-6
     x = x0.float().cuda()
-    ops.residual_add_rows(x, a.cuda(), None, mult=0.5)
-    assert rel(x, x0 + 0.5 * a.double()) < 1e-6
+    xc = ops.residual_add_rows(x, a.cuda(), None, mult=0.5, copy_dtype=BF)
+    assert rel(x, x0 + 0.5 * a.double()) < 1e-6 and torch.equal(xc, x.to(BF))
     x = x0.float().cuda()
     ops.add_row_vector(x, vec.float().cuda())
     assert rel(x, x0 + vec) < 1e-6

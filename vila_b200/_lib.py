@@ -135,6 +135,16 @@ class PagedAttnParams(C.Structure):
     ]
 
 
+class NormConvParams(C.Structure):
+    _fields_ = [
+        ("x", c_void_p), ("norm_w", c_void_p * 2), ("conv_w", c_void_p * 2), ("state", c_void_p * 2),
+        ("out", c_void_p * 2), ("seqs", c_void_p), ("row_seq", c_void_p),
+        ("conv_w_dtype", C.c_int32), ("out_dtype", C.c_int32), ("rows", C.c_int32), ("nseq", C.c_int32),
+        ("cols", C.c_int32), ("groups", C.c_int32), ("taps", C.c_int32), ("nsub", C.c_int32),
+        ("eps", c_float), ("w_offset", c_float),
+    ]
+
+
 # name -> argtypes; every function returns int (0 == ok) unless listed in _RESTYPES
 SIGNATURES = {
     "vila_abi_version": [],
@@ -198,11 +208,12 @@ SIGNATURES = {
     "vila_paged_attention": [C.POINTER(PagedAttnParams), c_void_p],
     "vila_moe_route_sigmoid": [c_void_p, c_int, c_i64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_int, c_void_p],
-    "vila_residual_add_rows": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_i64, c_int, c_float, c_int,
-                               c_int, c_void_p],
+    "vila_residual_add_rows": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_i64, c_int, c_float, c_void_p,
+                               c_int, c_int, c_int, c_void_p],
+    "vila_norm_conv_rows": [C.POINTER(NormConvParams), c_void_p],
     "vila_gated_norm_residual_scaled": [c_void_p, c_void_p, c_int, c_i64, c_int, c_void_p, c_int, c_i64, c_void_p,
                                         c_int, c_void_p, c_int, c_float, c_float, c_float, c_int, c_int, c_void_p],
-    "vila_gelu_mul_gather": [c_void_p, c_void_p, c_int, c_i64, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+    "vila_gelu_mul_gather": [c_void_p, c_int, c_void_p, c_int, c_i64, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
                              c_void_p],
 }
 _RESTYPES = {"vila_last_error": C.c_char_p}

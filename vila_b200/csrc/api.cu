@@ -446,10 +446,16 @@ int vila_moe_route_sigmoid(const void* x, int x_dtype, int64_t ldx, const float*
 }
 
 int vila_residual_add_rows(float* x, const void* a, int a_dtype, int64_t lda, const void* part,
-                           int part_dtype, int64_t ldp, int n_partials, float mult, int rows, int cols,
-                           void* stream) {
+                           int part_dtype, int64_t ldp, int n_partials, float mult, void* copy,
+                           int copy_dtype, int rows, int cols, void* stream) {
   VB_REQUIRE_DEVICE();
-  return vb::residual_add_rows(x, a, a_dtype, lda, part, part_dtype, ldp, n_partials, mult, rows, cols, st(stream));
+  return vb::residual_add_rows(x, a, a_dtype, lda, part, part_dtype, ldp, n_partials, mult, copy, copy_dtype, rows,
+                               cols, st(stream));
+}
+
+int vila_norm_conv_rows(const vila_norm_conv_params* p, void* stream) {
+  VB_REQUIRE_DEVICE();
+  return vb::norm_conv_rows(*p, st(stream));
 }
 
 int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, int64_t ldp, int n_partials,
@@ -461,11 +467,11 @@ int vila_gated_norm_residual_scaled(float* x, const void* part, int part_dtype, 
                                  bias_dtype, w, w_dtype, w_offset, eps, rows, cols, st(stream), mult);
 }
 
-int vila_gelu_mul_gather(const float* z, const void* table, int table_dtype, int64_t ld_table,
+int vila_gelu_mul_gather(const void* z, int z_dtype, const void* table, int table_dtype, int64_t ld_table,
                          const int32_t* ids, int col0, void* out, int out_dtype, int rows, int cols,
                          void* stream) {
   VB_REQUIRE_DEVICE();
-  return vb::gelu_mul_gather(z, table, table_dtype, ld_table, ids, col0, out, out_dtype, rows, cols, st(stream));
+  return vb::gelu_mul_gather(z, z_dtype, table, table_dtype, ld_table, ids, col0, out, out_dtype, rows, cols, st(stream));
 }
 
 }  // extern "C"

@@ -237,8 +237,8 @@ int embed_pair_rows(const void* table, int dt, const void* pair, int pdt, const 
                     int rows, int cols, cudaStream_t stream);
 int add_row_vector(float* x, const void* vec, int dt, int rows, int cols, cudaStream_t stream);
 int residual_add_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp,
-                      int np, float mult, int rows, int cols, cudaStream_t stream);
-int gelu_mul_gather(const float* z, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
+                      int np, float mult, void* copy, int c_dt, int rows, int cols, cudaStream_t stream);
+int gelu_mul_gather(const void* z, int z_dt, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
                     void* out, int o_dt, int rows, int cols, cudaStream_t stream);
 int moe_route_sigmoid(const void* x, int x_dt, int64_t ldx, const float* wr, const float* corr, int32_t* idx,
                       float* weight, int rows, int cols, int experts, int top, int groups, int keep,
@@ -260,7 +260,9 @@ struct vila_sink_attn_params;
 struct vila_glinear_ext;
 struct vila_rope_append_params;
 struct vila_paged_attn_params;
+struct vila_norm_conv_params;
 namespace vb {
+int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream);
 int rope_append(const vila_rope_append_params& p, cudaStream_t stream);
 int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream);
 int sink_attention(const vila_sink_attn_params& p, cudaStream_t stream);

@@ -230,8 +230,8 @@ add_row_vector_kernel(float* __restrict__ x, const void* __restrict__ vec, int d
 // x += mult * (a + sum_j part_j): the sum runs in a fixed order (a first, then the partials by index)
 __global__ void __launch_bounds__(kRowThreads)
 residual_add_rows_kernel(float* __restrict__ x, const void* __restrict__ a, int a_dt, int64_t lda,
-                         const void* __restrict__ part, int p_dt, int64_t ldp, int np, float mult, int rows,
-                         int cols) {
+                         const void* __restrict__ part, int p_dt, int64_t ldp, int np, float mult,
+                         void* __restrict__ copy, int c_dt, int rows, int cols) {
   const size_t total = static_cast<size_t>(rows) * cols;
   for (size_t i = blockIdx.x * static_cast<size_t>(kRowThreads) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * kRowThreads) {
@@ -239,19 +239,21 @@ residual_add_rows_kernel(float* __restrict__ x, const void* __restrict__ a, int 
     float y = a ? ld_any(a, a_dt, r * lda + c) : 0.f;
     if (part)
       for (int j = 0; j < np; ++j) y += ld_any(part, p_dt, (r * np + j) * ldp + c);
-    x[i] += mult * y;
+    const float v = x[i] + mult * y;
+    x[i] = v;
+    if (copy) st_any(copy, c_dt, i, v);
   }
 }
 
 __global__ void __launch_bounds__(kRowThreads)
-gelu_mul_gather_kernel(const float* __restrict__ z, const void* __restrict__ table, int dt, int64_t ldt,
+gelu_mul_gather_kernel(const void* __restrict__ z, int z_dt, const void* __restrict__ table, int dt, int64_t ldt,
                        const int32_t* __restrict__ ids, int col0, void* __restrict__ out, int o_dt, int rows,
                        int cols) {
   const size_t total = static_cast<size_t>(rows) * cols;
   for (size_t i = blockIdx.x * static_cast<size_t>(kRowThreads) + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * kRowThreads) {
     const size_t r = i / cols, c = i % cols;
-    const float v = z[i];
+    const float v = ld_any(z, z_dt, i);
     const float g = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
     st_any(out, o_dt, i, g * ld_any(table, dt, static_cast<size_t>(ids[r]) * ldt + col0 + c));
   }
@@ -426,19 +428,19 @@ int add_row_vector(float* x, const void* vec, int dt, int rows, int cols, cudaSt
 }
 
 int residual_add_rows(float* x, const void* a, int a_dt, int64_t lda, const void* part, int p_dt, int64_t ldp,
-                      int np, float mult, int rows, int cols, cudaStream_t stream) {
+                      int np, float mult, void* copy, int c_dt, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   VB_CHECK(part == nullptr || np >= 1, "residual_add_rows: n_partials=%d", np);
   VB_CUDA(launch_serial(residual_add_rows_kernel, dim3(flat_grid(static_cast<size_t>(rows) * cols)),
-                        dim3(kRowThreads), 0, stream, x, a, a_dt, lda, part, p_dt, ldp, np, mult, rows, cols));
+                        dim3(kRowThreads), 0, stream, x, a, a_dt, lda, part, p_dt, ldp, np, mult, copy, c_dt, rows, cols));
   return 0;
 }
 
-int gelu_mul_gather(const float* z, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
+int gelu_mul_gather(const void* z, int z_dt, const void* table, int dt, int64_t ldt, const int32_t* ids, int col0,
                     void* out, int o_dt, int rows, int cols, cudaStream_t stream) {
   if (rows <= 0 || cols <= 0) return 0;
   VB_CUDA(launch_serial(gelu_mul_gather_kernel, dim3(flat_grid(static_cast<size_t>(rows) * cols)),
-                        dim3(kRowThreads), 0, stream, z, table, dt, ldt, ids, col0, out, o_dt, rows, cols));
+                        dim3(kRowThreads), 0, stream, z, z_dt, table, dt, ldt, ids, col0, out, o_dt, rows, cols));
   return 0;
 }
 

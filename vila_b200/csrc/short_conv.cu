@@ -63,6 +63,91 @@ short_conv_state_kernel(const float* __restrict__ h, float* __restrict__ state, 
   }
 }
 
+
+// ---- group norm + short convolution for up to two sublayers in one pass ------------------------------
+// One CTA per row t.  Phase 1: the inverse root mean square of every piece of the rows t - back .. t that
+// lie inside the portion (a warp per (row, piece); the rows come from L2, they were just written).  Phase
+// 2: per channel, the taps of both sublayers from the normalised rows (x * inv) * norm weight, or from the
+// sequence's state for rows before the portion.  Same arithmetic as the separate kernels.
+__device__ __forceinline__ float piece_inv(const float* __restrict__ xr, int gc, float eps) {
+  float ss = 0.f;
+  for (int c = threadIdx.x & 31; c < gc; c += 32) ss = fmaf(xr[c], xr[c], ss);
+  ss = warp_sum(ss);
+  return 1.0f / sqrtf(ss / static_cast<float>(gc) + eps);
+}
+
+__global__ void __launch_bounds__(kThreads) norm_conv_rows_kernel(const vila_norm_conv_params p) {
+  extern __shared__ float inv_s[];   // [rows in reach][groups]
+  const int t = blockIdx.x, cols = p.cols, groups = p.groups, gc = cols / groups, taps = p.taps, back = taps - 1;
+  const int* sq = p.seqs + 4 * p.row_seq[t];
+  const int row0 = sq[0], pos0 = sq[2], slot = sq[3];
+  const int pos = pos0 + (t - row0);
+  const int n_in = min(back, t - row0);          // predecessors inside the portion
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pair = warp; pair < (n_in + 1) * groups; pair += kThreads / 32) {
+    const int k = pair / groups, piece = pair - k * groups;
+    const float r = piece_inv(p.x + static_cast<size_t>(t - k) * cols + static_cast<size_t>(piece) * gc, gc, p.eps);
+    if (lane == 0) inv_s[pair] = r;
+  }
+  __syncthreads();
+  const size_t soff = static_cast<size_t>(slot) * back * cols;
+  for (int c = threadIdx.x; c < cols; c += kThreads) {
+    const int piece = c / gc;
+    float w[2], acc[2] = {0.f, 0.f}, cur[2] = {0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < 2; ++k) w[k] = k < p.nsub ? p.norm_w[k][c] + p.w_offset : 0.f;
+    for (int d = 0; d <= back; ++d) {            // this tap looks d positions back; weight column back - d
+      if (pos - d < 0) break;
+      const bool inside = d <= n_in;
+      const float xn = inside ? p.x[static_cast<size_t>(t - d) * cols + c] * inv_s[d * groups + piece] : 0.f;
+#pragma unroll
+      for (int k = 0; k < 2; ++k) {
+        if (k < p.nsub) {
+          const float v = inside ? xn * w[k]
+                                 : p.state[k][soff + static_cast<size_t>(back - (d - (t - row0))) * cols + c];
+          if (d == 0) cur[k] = v;
+          acc[k] = fmaf(ld_any(p.conv_w[k], p.conv_w_dtype, static_cast<size_t>(c) * taps + (back - d)), v, acc[k]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+      if (k < p.nsub) st_any(p.out[k], p.out_dtype, static_cast<size_t>(t) * cols + c, cur[k] + acc[k]);
+  }
+}
+
+// One CTA per sequence: its last taps - 1 normalised inputs, for both sublayers.
+__global__ void __launch_bounds__(kThreads) norm_conv_state_kernel(const vila_norm_conv_params p) {
+  extern __shared__ float inv_s[];   // [rows kept][groups]
+  const int cols = p.cols, groups = p.groups, gc = cols / groups, back = p.taps - 1;
+  const int* sq = p.seqs + 4 * blockIdx.x;
+  const int row0 = sq[0], n = sq[1], pos0 = sq[2], slot = sq[3];
+  const int keep = min(back, n);                 // rows of the portion that enter the state: the last `keep`
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pair = warp; pair < keep * groups; pair += kThreads / 32) {
+    const int k = pair / groups, piece = pair - k * groups;     // k-th of the kept rows: row0 + n - keep + k
+    const float r = piece_inv(p.x + static_cast<size_t>(row0 + n - keep + k) * cols + static_cast<size_t>(piece) * gc, gc, p.eps);
+    if (lane == 0) inv_s[pair] = r;
+  }
+  __syncthreads();
+  const size_t soff = static_cast<size_t>(slot) * back * cols;
+  for (int c = threadIdx.x; c < cols; c += kThreads) {
+    const int piece = c / gc;
+    for (int j = 0; j < back; ++j) {
+      const int q = pos0 + n - back + j;          // position held by new state row j
+      const bool fresh = q >= pos0;
+      const int k = j - (back - keep);            // index among the kept rows
+      const float xn = fresh ? p.x[static_cast<size_t>(row0 + n - keep + k) * cols + c] * inv_s[k * groups + piece] : 0.f;
+      for (int u = 0; u < p.nsub; ++u) {
+        float v = 0.f;
+        if (fresh) v = xn * (p.norm_w[u][c] + p.w_offset);
+        else if (q >= 0) v = p.state[u][soff + static_cast<size_t>(j + n) * cols + c];
+        p.state[u][soff + static_cast<size_t>(j) * cols + c] = v;
+      }
+    }
+  }
+}
+
 }  // namespace
 
 int short_conv_rows(const float* h, const void* w, int w_dt, const float* state, const int32_t* seqs,
@@ -82,6 +167,20 @@ int short_conv_state(const float* h, float* state, const int32_t* seqs, int nseq
   VB_CHECK(taps <= kMaxTaps, "short_conv_state: taps=%d", taps);
   const dim3 grid(nseq, (cols + 4 * kThreads - 1) / (4 * kThreads));
   VB_CUDA(launch_serial(short_conv_state_kernel, grid, dim3(kThreads), 0, stream, h, state, seqs, cols, taps));
+  return 0;
+}
+
+int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream) {
+  if (p.rows <= 0 || p.cols <= 0) return 0;
+  VB_CHECK(p.taps >= 1 && p.taps <= kMaxTaps && p.groups >= 1 && p.cols % p.groups == 0 && (p.nsub == 1 || p.nsub == 2),
+           "norm_conv_rows: taps=%d groups=%d cols=%d nsub=%d", p.taps, p.groups, p.cols, p.nsub);
+  for (int k = 0; k < p.nsub; ++k)
+    VB_CHECK(p.norm_w[k] && p.conv_w[k] && p.out[k] && (p.taps == 1 || p.state[k]), "norm_conv_rows: sublayer %d lacks a tensor", k);
+  const size_t smem = sizeof(float) * p.taps * p.groups;
+  VB_CHECK(smem <= 48 * 1024, "norm_conv_rows: groups=%d", p.groups);
+  VB_CUDA(launch_serial(norm_conv_rows_kernel, dim3(p.rows), dim3(kThreads), smem, stream, p));
+  if (p.taps > 1 && p.nseq > 0)
+    VB_CUDA(launch_serial(norm_conv_state_kernel, dim3(p.nseq), dim3(kThreads), smem, stream, p));
   return 0;
 }
 

@@ -305,11 +305,17 @@ class LufatarForCausalLM:
                 for k in range(2 if self.config.layers[i].mlp_kind else 1)}
 
     # ---- compute --------------------------------------------------------------------------------------
-    def _sublayer_input(self, x, norm_w, canon_w, state, batch):
-        """group norm -> + causal short convolution (reads and then replaces the sequence's conv state)"""
+    def _sublayer_inputs(self, L: _Layer, x, batch, cache, run: int):
+        """group norm -> + causal short convolution, for the mixer and (if any) the feed-forward at once;
+        reads and then advances the sequences' convolution states"""
         cfg = self.config
-        h = ops.rmsnorm_rows(x, norm_w, cfg.norm_eps, groups=cfg.norm_groups, out_dtype=torch.float32)
-        return ops.short_conv_rows(h, canon_w, state, batch.seqs, batch.row_seq, out_dtype=self.dtype)
+        norms, convs = [L.norm1], [L.canon1]
+        if L.cfg.mlp_kind is not None:
+            norms.append(L.norm2)
+            convs.append(L.canon2)
+        return ops.norm_conv_rows(x, norms, convs, [cache.state.get((run, k)) for k in range(len(norms))],
+                                  batch.seqs, batch.row_seq,
+                                  groups=cfg.norm_groups, eps=cfg.norm_eps, out_dtype=self.dtype)
 
     def _attention(self, L: _Layer, a, batch, cache, run: int):
         lc = L.cfg
@@ -337,11 +343,12 @@ class LufatarForCausalLM:
         return ops.glinear(act, L.down, groups=lc.experts, seg=seg, o_rows=srt, row_scale=wt.view(-1),
                            out_dtype=torch.float32, out_rows_total=T * lc.top)
 
-    def _token_side(self, L: _Layer, x, batch):
+    def _token_side(self, L: _Layer, x, xc, batch):
+        """xc: x in the compute dtype (the gate projection's operand)"""
         cfg = self.config
-        z = ops.glinear(x, L.side_gate, out_dtype=torch.float32)
+        z = ops.linear_any(xc, L.side_gate)
         g = ops.gelu_mul_gather(z, self.side_embed, batch.ids, L.index * cfg.side_dim, out_dtype=self.dtype)
-        y = ops.glinear(g, L.side_proj, out_dtype=torch.float32)
+        y = ops.linear_any(g, L.side_proj)
         ops.gated_norm_residual(x, y, w=L.side_norm, eps=cfg.norm_eps, mult=cfg.residual_mult)
 
     @torch.inference_mode()
@@ -354,15 +361,15 @@ class LufatarForCausalLM:
             L = self.layers[i]
             if t >= 0 and i == cfg.loop_start:
                 ops.add_row_vector(x, self.loop_step[t])
-            a1 = self._sublayer_input(x, L.norm1, L.canon1, cache.state.get((run, 0)), batch)
-            y = self._attention(L, a1, batch, cache, run)
+            a = self._sublayer_inputs(L, x, batch, cache, run)
+            y = self._attention(L, a[0], batch, cache, run)
             parts, nparts = None, 1
             if L.cfg.mlp_kind is not None:
-                a2 = self._sublayer_input(x, L.norm2, L.canon2, cache.state.get((run, 1)), batch)
-                parts, nparts = self._experts(L, a2), L.cfg.top
-            ops.residual_add_rows(x, y, parts, n_partials=nparts, mult=cfg.residual_mult)
+                parts, nparts = self._experts(L, a[1]), L.cfg.top
+            xc = ops.residual_add_rows(x, y, parts, n_partials=nparts, mult=cfg.residual_mult,
+                                       copy_dtype=self.dtype if cfg.side_dim else None)
             if cfg.side_dim:
-                self._token_side(L, x, batch)
+                self._token_side(L, x, xc, batch)
             if layer_outputs is not None:
                 layer_outputs.append(x.clone())
         return x

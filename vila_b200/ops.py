@@ -678,6 +678,35 @@ def short_conv_rows(h: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tens
     return out
 
 
+def norm_conv_rows(x: torch.Tensor, norm_w: Sequence[torch.Tensor], conv_w: Sequence[torch.Tensor],
+                   state: Sequence[Optional[torch.Tensor]], seqs: torch.Tensor, row_seq: torch.Tensor, *,
+                   groups: int, eps: float, w_offset: float = 0.0, out_dtype=None):
+    """Group RMS norm of x fp32 [T, C] followed by `h + short convolution(h)` for one or two sublayers that
+    read the same rows (norm_w / conv_w / state per sublayer), in one pass; the states are advanced.
+    -> list of outputs [T, C].  Equals rmsnorm_rows(groups=) + short_conv_rows per sublayer."""
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
+    T, Cc = x.shape
+    nsub, taps = len(norm_w), conv_w[0].shape[1]
+    assert nsub in (1, 2) and len(conv_w) == nsub and len(state) == nsub and Cc % groups == 0
+    outs = [torch.empty(T, Cc, dtype=out_dtype or x.dtype, device=x.device) for _ in range(nsub)]
+    p = _lib.NormConvParams()
+    p.x = _p(x)
+    for k in range(nsub):
+        assert conv_w[k].shape == (Cc, taps) and conv_w[k].is_contiguous() and conv_w[k].dtype == conv_w[0].dtype
+        p.norm_w[k], p.conv_w[k], p.out[k] = _f32(norm_w[k], "norm_w"), _p(conv_w[k]), _p(outs[k])
+        if taps > 1:
+            st = state[k]
+            assert st is not None and st.dtype == torch.float32 and st.is_contiguous() and \
+                tuple(st.shape[1:]) == (taps - 1, Cc)
+            p.state[k] = _p(st)
+    p.seqs, p.row_seq = _i32(seqs, "seqs"), _i32(row_seq, "row_seq")
+    p.conv_w_dtype, p.out_dtype = _dt(conv_w[0], "conv_w"), _dt(outs[0], "out")
+    p.rows, p.nseq, p.cols, p.groups, p.taps, p.nsub = T, seqs.shape[0], Cc, groups, taps, nsub
+    p.eps, p.w_offset = eps, w_offset
+    check(_lib.load().vila_norm_conv_rows(C.byref(p), _stream()), "vila_norm_conv_rows")
+    return outs
+
+
 def rope_append(qkv: torch.Tensor, positions: torch.Tensor, cache_rows: torch.Tensor, pool: torch.Tensor, *,
                 heads: int, kv_heads: int, dim: int, vdim: int, inv_freq: Optional[torch.Tensor],
                 unit_norm: bool, eps: float) -> torch.Tensor:
@@ -753,26 +782,30 @@ def moe_route_sigmoid(x: torch.Tensor, w_router: torch.Tensor, correction: Optio
 
 
 def residual_add_rows(x: torch.Tensor, a: Optional[torch.Tensor] = None, part: Optional[torch.Tensor] = None, *,
-                      n_partials: int = 1, mult: float = 1.0) -> None:
-    """x fp32 [rows, cols] (in place) += mult * (a[r] + sum_j part[r * n_partials + j])"""
+                      n_partials: int = 1, mult: float = 1.0, copy_dtype=None) -> Optional[torch.Tensor]:
+    """x fp32 [rows, cols] (in place) += mult * (a[r] + sum_j part[r * n_partials + j]); copy_dtype: also
+    return the updated rows in that dtype (the operand of the projection that reads x next)."""
     assert x.dtype == torch.float32 and x.is_contiguous() and x.dim() == 2
     rows, cols = x.shape
     if a is not None:
         assert a.shape == (rows, cols) and a.stride(1) == 1
     if part is not None:
         assert part.shape == (rows * n_partials, cols) and part.stride(1) == 1
+    copy = torch.empty(rows, cols, dtype=copy_dtype, device=x.device) if copy_dtype is not None else None
     check(_lib.load().vila_residual_add_rows(
         _p(x), _p(a), _dt(a, "a") if a is not None else 0, a.stride(0) if a is not None else 0,
         _p(part), _dt(part, "part") if part is not None else 0, part.stride(0) if part is not None else 0,
-        n_partials, mult, rows, cols, _stream()), "vila_residual_add_rows")
+        n_partials, mult, _p(copy), _dt(copy, "copy") if copy is not None else 0, rows, cols, _stream()),
+        "vila_residual_add_rows")
+    return copy
 
 
 def gelu_mul_gather(z: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int, *, out_dtype=None) -> torch.Tensor:
-    """gelu_tanh(z fp32 [T, n]) * table[ids, col0 : col0 + n]"""
-    assert z.dtype == torch.float32 and z.is_contiguous() and z.dim() == 2
+    """gelu_tanh(z [T, n]) * table[ids, col0 : col0 + n]"""
+    assert z.is_contiguous() and z.dim() == 2
     assert table.dim() == 2 and table.stride(1) == 1 and col0 + z.shape[1] <= table.shape[1]
     out = torch.empty(z.shape, dtype=out_dtype or z.dtype, device=z.device)
-    check(_lib.load().vila_gelu_mul_gather(_p(z), _p(table), _dt(table, "table"), table.stride(0), _i32(ids, "ids"),
+    check(_lib.load().vila_gelu_mul_gather(_p(z), _dt(z, "z"), _p(table), _dt(table, "table"), table.stride(0), _i32(ids, "ids"),
                                            col0, _p(out), _dt(out, "out"), z.shape[0], z.shape[1], _stream()),
           "vila_gelu_mul_gather")
     return out
