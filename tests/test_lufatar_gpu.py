@@ -354,7 +354,8 @@ def make_pool(seq_kv, page, n_pages, dtype, seed=0):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
-@pytest.mark.parametrize("H,G,dk,dv", [(3, 3, 12, 20), (4, 1, 10, 6), (6, 2, 6, 10), (16, 4, 64, 64), (1, 1, 130, 5), (40, 8, 16, 24)])
+@pytest.mark.parametrize("H,G,dk,dv", [(3, 3, 12, 20), (4, 1, 10, 6), (6, 2, 6, 10), (16, 4, 64, 64), (1, 1, 130, 5), (40, 8, 16, 24),
+                                         (8, 2, 128, 128), (32, 8, 128, 128)])
 def test_paged_attention(cuda, dtype, H, G, dk, dv):
     """Two sequences in one launch; portions that start and end inside pages; single decoded rows with the
     keys split over 1, 3 and 16 CTAs; with and without head mixing and sink."""

@@ -26,6 +26,10 @@ constexpr int kWarps = kThreads / 32;
 constexpr float kNegBig = -1e30f;
 
 __host__ __device__ __forceinline__ int round4(int r) { return (r + 3) & ~3; }
+// Floats between the K rows of consecutive keys in shared memory: all G heads of a key (G * DS, DS = D4 + 4)
+// plus a pad that makes the stride 4 mod 32, so that the float4 reads of 8 consecutive keys (same head, same
+// column) fall into 8 different bank groups.
+__host__ __device__ __forceinline__ int key_stride(int G, int DS) { return G * DS + ((36 - (G * DS) % 32) % 32); }
 
 // ---- rotary + unit norm + append ---------------------------------------------------------------------
 // One CTA per token; warp w takes the heads w, w + 8, ... of q then k; v is copied by all threads.
@@ -90,18 +94,19 @@ __device__ __forceinline__ size_t pool_row(const int32_t* pt, int page, int j) {
 // K | V rows of a key block, widened to fp32: one warp per key.  16-byte loads when the head sizes allow
 // (bf16: multiples of 8, fp32: multiples of 4; the pool row is then 16-byte aligned as well).
 __device__ __forceinline__ void load_kv_block(float* Ks, float* Vs, const vila_paged_attn_params& p,
-                                              const int32_t* pt, int j0, int nkeys, int BK, int D4, int DS, int V4) {
+                                              const int32_t* pt, int j0, int nkeys, int BK, int D4, int DS, int V4,
+                                              int nwarps = kWarps) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int G = p.G, D = p.dim, V = p.vdim;
+  const int G = p.G, D = p.dim, V = p.vdim, KS = key_stride(p.G, DS);
   const size_t prw = static_cast<size_t>(G) * (D + V);
   const bool vec16 = p.pool_dtype == VILA_DT_BF16 && (D & 7) == 0 && (V & 7) == 0;
   const bool vec32 = p.pool_dtype == VILA_DT_F32 && (D & 3) == 0 && (V & 3) == 0;
-  for (int jj = warp; jj < BK; jj += kWarps) {
+  for (int jj = warp; jj < BK; jj += nwarps) {
     const int j = j0 + jj;
-    float* kd = Ks + jj * G * DS;
+    float* kd = Ks + jj * KS;
     float* vd = Vs + jj * G * V4;
     if (j >= nkeys) {
-      for (int x = lane; x < G * DS; x += 32) kd[x] = 0.f;
+      for (int x = lane; x < KS; x += 32) kd[x] = 0.f;
       for (int x = lane; x < G * V4; x += 32) vd[x] = 0.f;
       continue;
     }
@@ -157,10 +162,10 @@ template <int NACC>
 __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_attn_params p, const AttnShape sh) {
   extern __shared__ __align__(16) float sm[];
   const int H = p.H, G = p.G, D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK;
-  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, rep = H / G;
+  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, rep = H / G, KS = key_stride(G, DS);
   float* Qs = sm;
   float* Ks = Qs + R * D4;
-  float* Vs = Ks + BK * G * DS;
+  float* Vs = Ks + BK * KS;
   float* Ss = Vs + BK * G * V4;
   float* Ps = Ss + R * BK;
   float* Tk = Ps + R * BK;
@@ -204,7 +209,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
     for (int idx = tid; idx < R * BK; idx += kThreads) {
       const int r = idx / BK, jj = idx - r * BK, h = r % H;
       const float4* qr = reinterpret_cast<const float4*>(Qs + r * D4);
-      const float4* kr = reinterpret_cast<const float4*>(Ks + (jj * G + h / rep) * DS);
+      const float4* kr = reinterpret_cast<const float4*>(Ks + jj * KS + (h / rep) * DS);
       float s = 0.f;
 #pragma unroll 4
       for (int k = 0; k < (D4 >> 2); ++k) {
@@ -285,20 +290,20 @@ __global__ void __launch_bounds__(kThreads) paged_attn_kernel(const vila_paged_a
 // Prompt portions: BQ (a multiple of 4) rows x all heads per CTA, register-tiled.  Score rows are ordered
 // head-major (r = h * BQ + i) so that 4 consecutive score rows are 4 query rows of ONE head: they share
 // the key / value head, and a thread that owns such a block of 4 keeps
-//   scores:        4 rows x 2 keys (keys jp and jp + BK / 2) per thread, q and k as float4 pieces: 6 shared
-//                  loads per 32 multiply-adds
+//   scores:        TR (4, or 2 with 512 threads) rows x 2 keys (jp and jp + BK / 2) per thread, q and k as float4
+//                  pieces: 6 shared loads per 32 multiply-adds (4 per 16)
 //   weighted sum:  4 rows x 4 value columns per accumulator, the 4 weights of a key as ONE float4
 //                  (Ps is [row block][key][4]): 2 shared loads per 16 multiply-adds
 // Shared memory (floats): Qs [R][D4] | Ks [BK][G][DS] | Vs [BK][G][V4] | Ss [R][BK] | Ps [R / 4][BK][4] |
 //   m, l, alpha [R] | talk [H * H]
-template <int NACC>
-__global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_paged_attn_params p, const AttnShape sh) {
+template <int NACC, int NT, int TR>
+__global__ void __launch_bounds__(NT) paged_attn_tile4_kernel(const vila_paged_attn_params p, const AttnShape sh) {
   extern __shared__ __align__(16) float sm[];
   const int H = p.H, G = p.G, D = p.dim, V = p.vdim, BQ = sh.BQ, BK = sh.BK, HK = sh.BK >> 1;
-  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, NB = R >> 2, rep = H / G;
+  const int D4 = round4(D), DS = D4 + 4, V4 = round4(V), R = BQ * H, NB = R >> 2, rep = H / G, KS = key_stride(G, DS);
   float* Qs = sm;
   float* Ks = Qs + R * D4;
-  float* Vs = Ks + BK * G * DS;
+  float* Vs = Ks + BK * KS;
   float* Ss = Vs + BK * G * V4;
   float* Ps = Ss + R * BK;
   float* m_s = Ps + R * BK;
@@ -313,12 +318,12 @@ __global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_p
   const int row0 = tile[0] + i0, n = min(BQ, n_tile - i0), pos0 = tile[2] + i0;
   const int32_t* pt = p.page_tables + static_cast<size_t>(tile[3]) * p.pt_stride;
 
-  for (int idx = tid; idx < R * D4; idx += kThreads) {
+  for (int idx = tid; idx < R * D4; idx += NT) {
     const int r = idx / D4, k = idx - r * D4, h = r / BQ, i = r - h * BQ;
     Qs[idx] = (i < n && k < D) ? p.q[(static_cast<size_t>(row0 + i) * H + h) * D + k] * p.scale : 0.f;
   }
-  for (int idx = tid; idx < H * H; idx += kThreads) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
-  for (int r = tid; r < R; r += kThreads) {
+  for (int idx = tid; idx < H * H; idx += NT) Tk[idx] = p.talk ? p.talk[idx] : ((idx / H) == (idx % H) ? 1.f : 0.f);
+  for (int r = tid; r < R; r += NT) {
     m_s[r] = p.sink ? p.sink[r / BQ] : kNegBig;
     l_s[r] = p.sink ? 1.0f : 0.0f;
   }
@@ -334,22 +339,22 @@ __global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_p
 
   for (int j0 = 0; j0 < nkeys; j0 += BK) {
     __syncthreads();
-    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4);
+    load_kv_block(Ks, Vs, p, pt, j0, nkeys, BK, D4, DS, V4, NT / 32);
     __syncthreads();
-    for (int item = tid; item < NB * HK; item += kThreads) {
-      const int rb = item / HK, jp = item - rb * HK;
-      const int g = ((rb << 2) / BQ) / rep;
-      const float4* q0 = reinterpret_cast<const float4*>(Qs + (rb << 2) * D4);
-      const float4* k0 = reinterpret_cast<const float4*>(Ks + (jp * G + g) * DS);
-      const float4* k1 = reinterpret_cast<const float4*>(Ks + ((jp + HK) * G + g) * DS);
-      float s[4][2];
+    for (int item = tid; item < (R / TR) * HK; item += NT) {
+      const int rbs = item / HK, jp = item - rbs * HK, r0 = rbs * TR;     // TR score rows of one head x 2 keys
+      const int g = (r0 / BQ) / rep;
+      const float4* q0 = reinterpret_cast<const float4*>(Qs + r0 * D4);
+      const float4* k0 = reinterpret_cast<const float4*>(Ks + jp * KS + g * DS);
+      const float4* k1 = reinterpret_cast<const float4*>(Ks + (jp + HK) * KS + g * DS);
+      float s[TR][2];
 #pragma unroll
-      for (int a = 0; a < 4; ++a) s[a][0] = s[a][1] = 0.f;
+      for (int a = 0; a < TR; ++a) s[a][0] = s[a][1] = 0.f;
 #pragma unroll 2
       for (int k = 0; k < d4n; ++k) {
         const float4 ka = k0[k], kb = k1[k];
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
+        for (int a = 0; a < TR; ++a) {
           const float4 qv = q0[a * d4n + k];
           s[a][0] = fmaf(qv.x, ka.x, s[a][0]); s[a][0] = fmaf(qv.y, ka.y, s[a][0]);
           s[a][0] = fmaf(qv.z, ka.z, s[a][0]); s[a][0] = fmaf(qv.w, ka.w, s[a][0]);
@@ -358,38 +363,75 @@ __global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_p
         }
       }
 #pragma unroll
-      for (int a = 0; a < 4; ++a) {
-        Ss[((rb << 2) + a) * BK + jp] = s[a][0];
-        Ss[((rb << 2) + a) * BK + jp + HK] = s[a][1];
+      for (int a = 0; a < TR; ++a) {
+        Ss[(r0 + a) * BK + jp] = s[a][0];
+        Ss[(r0 + a) * BK + jp + HK] = s[a][1];
       }
     }
     __syncthreads();
-    for (int r = warp; r < R; r += kWarps) {
-      const int h = r / BQ, i = r - h * BQ;
-      const bool valid = lane < BK && i < n && j0 + lane <= pos0 + i;
-      float s = 0.f;
-      if (lane < BK) {
-        const float* tk = Tk + h * H;
-        const float* sr = Ss + i * BK + lane;
-        for (int g = 0; g < H; ++g) s = fmaf(tk[g], sr[g * BQ * BK], s);
+    // head mixing + mask + online softmax: a warp takes 4 score rows at a time (rows warp, warp + 8, ...), a
+    // lane per key; the 4 rows' reductions are interleaved so that their shuffles overlap
+    for (int rbase = warp; rbase < R; rbase += 4 * (NT / 32)) {
+      float sv[4], mo[4], mn[4], pj[4], ps[4];
+      bool ok[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = rbase + u * (NT / 32);
+        sv[u] = kNegBig;
+        ok[u] = false;
+        mo[u] = kNegBig;
+        if (r < R) {
+          const int h = r / BQ, i = r - h * BQ;
+          ok[u] = lane < BK && i < n && j0 + lane <= pos0 + i;
+          if (lane < BK) {
+            const float* tk = Tk + h * H;
+            const float* sr = Ss + i * BK + lane;
+            float s0 = 0.f, s1 = 0.f;
+            int g = 0;
+            for (; g + 1 < H; g += 2) {
+              s0 = fmaf(tk[g], sr[g * BQ * BK], s0);
+              s1 = fmaf(tk[g + 1], sr[(g + 1) * BQ * BK], s1);
+            }
+            if (g < H) s0 = fmaf(tk[g], sr[g * BQ * BK], s0);
+            if (ok[u]) sv[u] = s0 + s1;
+          }
+          mo[u] = m_s[r];
+        }
       }
-      s = valid ? s : kNegBig;
-      const float m_old = m_s[r];
-      const float m_new = fmaxf(m_old, warp_max(s));
-      const float pj = valid ? expf(s - m_new) : 0.f;
-      const float ps = warp_sum(pj);
-      if (lane < BK) Ps[(((r >> 2) * BK + lane) << 2) + (r & 3)] = pj;
-      if (lane == 0) {
-        const float alpha = expf(m_old - m_new);
-        a_s[r] = alpha;
-        l_s[r] = l_s[r] * alpha + ps;
-        m_s[r] = m_new;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) mn[u] = sv[u];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mn[u] = fmaxf(mn[u], __shfl_xor_sync(0xffffffffu, mn[u], o));
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        mn[u] = fmaxf(mn[u], mo[u]);
+        pj[u] = ok[u] ? expf(sv[u] - mn[u]) : 0.f;
+        ps[u] = pj[u];
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int u = 0; u < 4; ++u) ps[u] += __shfl_xor_sync(0xffffffffu, ps[u], o);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = rbase + u * (NT / 32);
+        if (r < R) {
+          if (lane < BK) Ps[(((r >> 2) * BK + lane) << 2) + (r & 3)] = pj[u];
+          if (lane == 0) {
+            const float alpha = expf(mo[u] - mn[u]);
+            a_s[r] = alpha;
+            l_s[r] = l_s[r] * alpha + ps[u];
+            m_s[r] = mn[u];
+          }
+        }
       }
     }
     __syncthreads();
 #pragma unroll
     for (int a = 0; a < NACC; ++a) {
-      const int o = tid + a * kThreads;
+      const int o = tid + a * NT;
       if (o < nout) {
         const int rb = o / vq, c4 = o - rb * vq;
         const int g = ((rb << 2) / BQ) / rep;
@@ -418,7 +460,7 @@ __global__ void __launch_bounds__(kThreads) paged_attn_tile4_kernel(const vila_p
   __syncthreads();
 #pragma unroll
   for (int a = 0; a < NACC; ++a) {
-    const int o = tid + a * kThreads;
+    const int o = tid + a * NT;
     if (o >= nout) continue;
     const int rb = o / vq, c4 = o - rb * vq;
 #pragma unroll
@@ -455,7 +497,7 @@ __global__ void __launch_bounds__(128) paged_attn_merge_kernel(const vila_paged_
 
 size_t attn_smem(const vila_paged_attn_params& p, int BQ, int BK) {
   const int D4 = round4(p.dim), V4 = round4(p.vdim), R = BQ * p.H;
-  return sizeof(float) * (static_cast<size_t>(R) * D4 + static_cast<size_t>(BK) * p.G * (D4 + 4) +
+  return sizeof(float) * (static_cast<size_t>(R) * D4 + static_cast<size_t>(BK) * key_stride(p.G, D4 + 4) +
                           static_cast<size_t>(BK) * p.G * V4 + 2 * static_cast<size_t>(R) * BK + p.H * p.H + 3 * R);
 }
 
@@ -475,7 +517,7 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
   VB_CHECK(p.H >= 1 && p.G >= 1 && p.H % p.G == 0 && p.dim >= 1 && p.vdim >= 1 && p.page >= 1 && p.nsplit >= 1 &&
                p.nsplit <= 64 && (p.nsplit == 1 || p.partial != nullptr),
            "paged_attention: H=%d G=%d dim=%d vdim=%d page=%d nsplit=%d", p.H, p.G, p.dim, p.vdim, p.page, p.nsplit);
-  constexpr size_t kSmemMax = 200 * 1024;
+  constexpr size_t kSmemMax = 224 * 1024;
   VB_CHECK(p.max_rows >= 1 && p.max_rows <= 16 && (p.nsplit == 1 || p.max_rows == 1),
            "paged_attention: max_rows=%d nsplit=%d (key splitting serves one-row tiles)", p.max_rows, p.nsplit);
   AttnShape sh;
@@ -485,21 +527,27 @@ int paged_attention(const vila_paged_attn_params& p, cudaStream_t stream) {
     while (sh.BQ > 4 && sh.BQ * p.H > 64) sh.BQ >>= 1;
     sh.BK = 32;
     while (attn_smem(p, sh.BQ, sh.BK) > kSmemMax && sh.BK > 8) sh.BK >>= 1;
-    const int nacc4 = ((sh.BQ * p.H / 4) * (round4(p.vdim) >> 2) + kThreads - 1) / kThreads;
     const size_t smem4 = attn_smem(p, sh.BQ, sh.BK);
-    if (smem4 <= kSmemMax && nacc4 <= 4) {
+    const int items = (sh.BQ * p.H / 4) * (round4(p.vdim) >> 2);      // accumulator items (4 rows x 4 columns)
+    // 512 threads (16 warps on the SM, 2-row score tiles) when there is accumulator work for them
+    const int nt = items >= 512 ? 512 : 256;
+    const int nacc4 = (items + nt - 1) / nt;
+    if (smem4 <= kSmemMax && nacc4 <= (nt == 512 ? 2 : 4)) {
       sh.sub = (p.max_rows + sh.BQ - 1) / sh.BQ;
       const dim3 grid4(p.ntiles, sh.sub, 1);
-#define VB_PAGED4(N)                                                                                             \
+#define VB_PAGED4(N, NT, TR)                                                                                     \
   do {                                                                                                           \
     if (smem4 > 48 * 1024)                                                                                       \
-      VB_CUDA(cudaFuncSetAttribute(paged_attn_tile4_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
-                                   static_cast<int>(smem4)));                                                    \
-    VB_CUDA(launch_serial(paged_attn_tile4_kernel<N>, grid4, dim3(kThreads), smem4, stream, p, sh));             \
+      VB_CUDA(cudaFuncSetAttribute(paged_attn_tile4_kernel<N, NT, TR>,                                           \
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem4)));       \
+    VB_CUDA(launch_serial(paged_attn_tile4_kernel<N, NT, TR>, grid4, dim3(NT), smem4, stream, p, sh));           \
   } while (0)
-      if (nacc4 <= 1) VB_PAGED4(1);
-      else if (nacc4 <= 2) VB_PAGED4(2);
-      else VB_PAGED4(4);
+      if (nt == 512) {
+        if (nacc4 <= 1) VB_PAGED4(1, 512, 2);
+        else VB_PAGED4(2, 512, 2);
+      } else if (nacc4 <= 1) VB_PAGED4(1, 256, 4);
+      else if (nacc4 <= 2) VB_PAGED4(2, 256, 4);
+      else VB_PAGED4(4, 256, 4);
 #undef VB_PAGED4
       return 0;
     }
