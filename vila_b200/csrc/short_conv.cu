@@ -71,7 +71,17 @@ short_conv_state_kernel(const float* __restrict__ h, float* __restrict__ state, 
 // sequence's state for rows before the portion.  Same arithmetic as the separate kernels.
 __device__ __forceinline__ float piece_inv(const float* __restrict__ xr, int gc, float eps) {
   float ss = 0.f;
-  for (int c = threadIdx.x & 31; c < gc; c += 32) ss = fmaf(xr[c], xr[c], ss);
+  if ((gc & 3) == 0 && (reinterpret_cast<uintptr_t>(xr) & 15) == 0) {
+    const float4* x4 = reinterpret_cast<const float4*>(xr);
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+    for (int c = threadIdx.x & 31; c < (gc >> 2); c += 32) {
+      const float4 v = __ldg(x4 + c);
+      s0 = fmaf(v.x, v.x, s0); s1 = fmaf(v.y, v.y, s1); s2 = fmaf(v.z, v.z, s2); s3 = fmaf(v.w, v.w, s3);
+    }
+    ss = (s0 + s1) + (s2 + s3);
+  } else {
+    for (int c = threadIdx.x & 31; c < gc; c += 32) ss = fmaf(xr[c], xr[c], ss);
+  }
   ss = warp_sum(ss);
   return 1.0f / sqrtf(ss / static_cast<float>(gc) + eps);
 }
@@ -113,6 +123,92 @@ __global__ void __launch_bounds__(kThreads) norm_conv_rows_kernel(const vila_nor
 #pragma unroll
     for (int k = 0; k < 2; ++k)
       if (k < p.nsub) st_any(p.out[k], p.out_dtype, static_cast<size_t>(t) * cols + c, cur[k] + acc[k]);
+  }
+}
+
+// The same pass for the common layout (fp32 convolution weights, channel count and piece width multiples of 4,
+// 2 .. 4 taps): a thread owns 4 consecutive channels, the taps are unrolled, rows are read with 16-byte loads.
+template <int TAPS, int NSUB>
+__global__ void __launch_bounds__(kThreads) norm_conv_rows_vec_kernel(const vila_norm_conv_params p) {
+  extern __shared__ float inv_s[];   // [rows in reach][groups]
+  constexpr int back = TAPS - 1;
+  const int t = blockIdx.x, cols = p.cols, groups = p.groups, gc = cols / groups;
+  const int* sq = p.seqs + 4 * p.row_seq[t];
+  const int row0 = sq[0], pos0 = sq[2], slot = sq[3];
+  const int pos = pos0 + (t - row0);
+  const int n_in = min(back, t - row0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int pair = warp; pair < (n_in + 1) * groups; pair += kThreads / 32) {
+    const int k = pair / groups, piece = pair - k * groups;
+    const float r = piece_inv(p.x + static_cast<size_t>(t - k) * cols + static_cast<size_t>(piece) * gc, gc, p.eps);
+    if (lane == 0) inv_s[pair] = r;
+  }
+  __syncthreads();
+  const float* xrow[TAPS];
+  const float* srow[NSUB][TAPS];
+  bool live[TAPS], inside[TAPS];
+#pragma unroll
+  for (int d = 0; d < TAPS; ++d) {
+    live[d] = pos - d >= 0;
+    inside[d] = d <= n_in;
+    xrow[d] = p.x + static_cast<size_t>(inside[d] ? t - d : t) * cols;
+#pragma unroll
+    for (int k = 0; k < NSUB; ++k)
+      srow[k][d] = (live[d] && !inside[d])
+                       ? p.state[k] + (static_cast<size_t>(slot) * back + (back - (d - (t - row0)))) * cols
+                       : nullptr;
+  }
+  for (int c = threadIdx.x << 2; c < cols; c += kThreads << 2) {
+    const int piece = c / gc;
+    float nw[NSUB][4], acc[NSUB][4], cur[NSUB][4];
+#pragma unroll
+    for (int k = 0; k < NSUB; ++k) {
+      const float4 w4 = __ldg(reinterpret_cast<const float4*>(p.norm_w[k] + c));
+      nw[k][0] = w4.x + p.w_offset; nw[k][1] = w4.y + p.w_offset; nw[k][2] = w4.z + p.w_offset; nw[k][3] = w4.w + p.w_offset;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[k][e] = cur[k][e] = 0.f;
+    }
+#pragma unroll
+    for (int d = 0; d < TAPS; ++d) {
+      if (!live[d]) continue;
+      float xn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (inside[d]) {
+        const float4 xv = *reinterpret_cast<const float4*>(xrow[d] + c);
+        const float inv = inv_s[d * groups + piece];
+        xn[0] = xv.x * inv; xn[1] = xv.y * inv; xn[2] = xv.z * inv; xn[3] = xv.w * inv;
+      }
+#pragma unroll
+      for (int k = 0; k < NSUB; ++k) {
+        float v[4];
+        if (inside[d]) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = xn[e] * nw[k][e];
+        } else {
+          const float4 sv = *reinterpret_cast<const float4*>(srow[k][d] + c);
+          v[0] = sv.x; v[1] = sv.y; v[2] = sv.z; v[3] = sv.w;
+        }
+        const float* cw = static_cast<const float*>(p.conv_w[k]) + static_cast<size_t>(c) * TAPS + (back - d);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (d == 0) cur[k][e] = v[e];
+          acc[k][e] = fmaf(__ldg(cw + e * TAPS), v[e], acc[k][e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < NSUB; ++k) {
+      const size_t o = static_cast<size_t>(t) * cols + c;
+      const float r0 = cur[k][0] + acc[k][0], r1 = cur[k][1] + acc[k][1], r2 = cur[k][2] + acc[k][2], r3 = cur[k][3] + acc[k][3];
+      if (p.out_dtype == VILA_DT_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(p.out[k]) + o) = make_float4(r0, r1, r2, r3);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned int*>(&lo);
+        u.y = *reinterpret_cast<unsigned int*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out[k]) + o) = u;
+      }
+    }
   }
 }
 
@@ -178,7 +274,24 @@ int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream) {
     VB_CHECK(p.norm_w[k] && p.conv_w[k] && p.out[k] && (p.taps == 1 || p.state[k]), "norm_conv_rows: sublayer %d lacks a tensor", k);
   const size_t smem = sizeof(float) * p.taps * p.groups;
   VB_CHECK(smem <= 48 * 1024, "norm_conv_rows: groups=%d", p.groups);
-  VB_CUDA(launch_serial(norm_conv_rows_kernel, dim3(p.rows), dim3(kThreads), smem, stream, p));
+  bool aligned = p.conv_w_dtype == VILA_DT_F32 && p.cols % 4 == 0 && (p.cols / p.groups) % 4 == 0 && p.taps >= 2 &&
+                 p.taps <= 4 && reinterpret_cast<uintptr_t>(p.x) % 16 == 0;
+  for (int k = 0; k < p.nsub; ++k)
+    aligned = aligned && reinterpret_cast<uintptr_t>(p.norm_w[k]) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out[k]) % 16 == 0 &&
+              reinterpret_cast<uintptr_t>(p.state[k]) % 16 == 0;
+#define VB_NC(T, N) VB_CUDA(launch_serial(norm_conv_rows_vec_kernel<T, N>, dim3(p.rows), dim3(kThreads), smem, stream, p))
+  if (aligned && p.nsub == 2) {
+    if (p.taps == 2) VB_NC(2, 2);
+    else if (p.taps == 3) VB_NC(3, 2);
+    else VB_NC(4, 2);
+  } else if (aligned) {
+    if (p.taps == 2) VB_NC(2, 1);
+    else if (p.taps == 3) VB_NC(3, 1);
+    else VB_NC(4, 1);
+  } else {
+    VB_CUDA(launch_serial(norm_conv_rows_kernel, dim3(p.rows), dim3(kThreads), smem, stream, p));
+  }
+#undef VB_NC
   if (p.taps > 1 && p.nseq > 0)
     VB_CUDA(launch_serial(norm_conv_state_kernel, dim3(p.nseq), dim3(kThreads), smem, stream, p));
   return 0;
