@@ -548,6 +548,7 @@ typedef struct vila_norm_conv_params {
   void* out[2];          /* [rows, cols] */
   const int32_t* seqs;
   const int32_t* row_seq;
+  float* inv; /* scratch [rows, groups] (inverse root mean squares), or NULL: every CTA computes what it needs */
   int32_t conv_w_dtype, out_dtype, rows, nseq, cols, groups, taps, nsub;
   float eps, w_offset;
 } vila_norm_conv_params;

@@ -268,6 +268,39 @@ def test_fused_norm_and_short_conv_in_portions(cuda, dtype, taps, groups, nsub):
             assert rel(torch.cat(got[name][k]), want[name][k]) < 1e-5, (name, k)
 
 
+def test_fused_norm_conv_many_rows(cuda):
+    """steps of more than 256 rows take the streaming form (statistics kernel + channel-slice CTAs): two
+    sequences whose portions start inside the other's row blocks, states carried from step to step"""
+    ops = _ops()
+    C, taps, groups = 1040, 4, 2            # two channel slices, the second one partly empty
+    nw = [1 + rnd(C, seed=10 + k, scale=0.2) for k in range(2)]
+    cw = [rnd(C, taps, seed=20 + k, scale=0.5).float() for k in range(2)]
+    seqs = {"a": rnd(300, C, seed=4, scale=3.0).float(), "b": rnd(295, C, seed=5, scale=0.2).float()}
+    want = {n: [O.short_conv_residual(O.group_norm(v.double(), nw[k], groups, 1e-5), cw[k].double()) for k in range(2)]
+            for n, v in seqs.items()}
+    state = [torch.full((2, taps - 1, C), 55.0, device="cuda") for _ in range(2)]
+    got = {n: [[], []] for n in seqs}
+    at = {"a": 0, "b": 0}
+    for step in ([("a", 270), ("b", 5)], [("b", 290), ("a", 30)]):
+        rows, sq, rseq = [], [], []
+        for name, n in step:
+            sq.append((sum(r.shape[0] for r in rows), n, at[name], 0 if name == "a" else 1))
+            rseq += [len(sq) - 1] * n
+            rows.append(seqs[name][at[name]:at[name] + n])
+            at[name] += n
+        outs = ops.norm_conv_rows(torch.cat(rows).cuda(), [w.float().cuda() for w in nw], [w.cuda() for w in cw], state,
+                                  torch.tensor(sq, dtype=torch.int32).cuda(), torch.tensor(rseq, dtype=torch.int32).cuda(),
+                                  groups=groups, eps=1e-5, out_dtype=F32)
+        o = 0
+        for name, n in step:
+            for k in range(2):
+                got[name][k].append(outs[k][o:o + n].cpu())
+            o += n
+    for name in seqs:
+        for k in range(2):
+            assert rel(torch.cat(got[name][k]), want[name][k]) < 1e-5, (name, k)
+
+
 @pytest.mark.parametrize("dtype", [F32, BF])
 @pytest.mark.parametrize("H,G,dim,vdim,rot", [(3, 3, 12, 20, 8), (4, 1, 10, 6, 10), (2, 2, 16, 16, 0), (10, 2, 64, 32, 32)])
 def test_rope_append(cuda, dtype, H, G, dim, vdim, rot):

@@ -138,7 +138,7 @@ class PagedAttnParams(C.Structure):
 class NormConvParams(C.Structure):
     _fields_ = [
         ("x", c_void_p), ("norm_w", c_void_p * 2), ("conv_w", c_void_p * 2), ("state", c_void_p * 2),
-        ("out", c_void_p * 2), ("seqs", c_void_p), ("row_seq", c_void_p),
+        ("out", c_void_p * 2), ("seqs", c_void_p), ("row_seq", c_void_p), ("inv", c_void_p),
         ("conv_w_dtype", C.c_int32), ("out_dtype", C.c_int32), ("rows", C.c_int32), ("nseq", C.c_int32),
         ("cols", C.c_int32), ("groups", C.c_int32), ("taps", C.c_int32), ("nsub", C.c_int32),
         ("eps", c_float), ("w_offset", c_float),

@@ -212,6 +212,94 @@ __global__ void __launch_bounds__(kThreads) norm_conv_rows_vec_kernel(const vila
   }
 }
 
+// ---- the streaming form: statistics first, then CTAs that own a channel slice of a block of rows -------
+// group_inv_kernel: inv[row, piece] (a warp per pair).  norm_conv_slice_kernel: grid (row blocks, channel
+// slices of 4 * 256 channels); a thread keeps the convolution and norm weights of its 4 channels in
+// registers for all rows of the block, so the weights are read once per CTA instead of once per row, and
+// the predecessor rows a tap needs were read by the same thread one row earlier (L1).
+__global__ void __launch_bounds__(kThreads) group_inv_kernel(const vila_norm_conv_params p) {
+  const int gc = p.cols / p.groups;
+  const int pair = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (pair >= p.rows * p.groups) return;
+  const int row = pair / p.groups, piece = pair - row * p.groups;
+  const float r = piece_inv(p.x + static_cast<size_t>(row) * p.cols + static_cast<size_t>(piece) * gc, gc, p.eps);
+  if ((threadIdx.x & 31) == 0) p.inv[pair] = r;
+}
+
+template <int TAPS, int NSUB>
+__global__ void __launch_bounds__(kThreads) norm_conv_slice_kernel(const vila_norm_conv_params p, int RB) {
+  constexpr int back = TAPS - 1;
+  const int cols = p.cols, groups = p.groups, gc = cols / groups;
+  const int c = (blockIdx.y * kThreads + threadIdx.x) << 2;
+  if (c >= cols) return;
+  const int piece = c / gc;
+  const int t0 = blockIdx.x * RB, t1 = min(p.rows, t0 + RB);
+  float nw[NSUB][4], cw[NSUB][4][TAPS];
+#pragma unroll
+  for (int k = 0; k < NSUB; ++k) {
+    const float4 w4 = __ldg(reinterpret_cast<const float4*>(p.norm_w[k] + c));
+    nw[k][0] = w4.x + p.w_offset; nw[k][1] = w4.y + p.w_offset; nw[k][2] = w4.z + p.w_offset; nw[k][3] = w4.w + p.w_offset;
+    const float* w = static_cast<const float*>(p.conv_w[k]) + static_cast<size_t>(c) * TAPS;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+      for (int j = 0; j < TAPS; ++j) cw[k][e][j] = __ldg(w + e * TAPS + j);
+  }
+  for (int t = t0; t < t1; ++t) {
+    const int* sq = p.seqs + 4 * p.row_seq[t];
+    const int row0 = sq[0], pos0 = sq[2], slot = sq[3];
+    const int pos = pos0 + (t - row0);
+    const int n_in = min(back, t - row0);
+    float acc[NSUB][4], cur[NSUB][4];
+#pragma unroll
+    for (int k = 0; k < NSUB; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[k][e] = cur[k][e] = 0.f;
+#pragma unroll
+    for (int d = 0; d < TAPS; ++d) {
+      if (pos - d < 0) continue;
+      const bool inside = d <= n_in;
+      float xn[4] = {0.f, 0.f, 0.f, 0.f};
+      if (inside) {
+        const float4 xv = *reinterpret_cast<const float4*>(p.x + static_cast<size_t>(t - d) * cols + c);
+        const float inv = p.inv[(t - d) * groups + piece];
+        xn[0] = xv.x * inv; xn[1] = xv.y * inv; xn[2] = xv.z * inv; xn[3] = xv.w * inv;
+      }
+#pragma unroll
+      for (int k = 0; k < NSUB; ++k) {
+        float v[4];
+        if (inside) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[e] = xn[e] * nw[k][e];
+        } else {
+          const float4 sv = *reinterpret_cast<const float4*>(
+              p.state[k] + (static_cast<size_t>(slot) * back + (back - (d - (t - row0)))) * cols + c);
+          v[0] = sv.x; v[1] = sv.y; v[2] = sv.z; v[3] = sv.w;
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (d == 0) cur[k][e] = v[e];
+          acc[k][e] = fmaf(cw[k][e][back - d], v[e], acc[k][e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < NSUB; ++k) {
+      const size_t o = static_cast<size_t>(t) * cols + c;
+      const float r0 = cur[k][0] + acc[k][0], r1 = cur[k][1] + acc[k][1], r2 = cur[k][2] + acc[k][2], r3 = cur[k][3] + acc[k][3];
+      if (p.out_dtype == VILA_DT_F32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(p.out[k]) + o) = make_float4(r0, r1, r2, r3);
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(r0, r1), hi = __floats2bfloat162_rn(r2, r3);
+        uint2 u;
+        u.x = *reinterpret_cast<unsigned int*>(&lo);
+        u.y = *reinterpret_cast<unsigned int*>(&hi);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(p.out[k]) + o) = u;
+      }
+    }
+  }
+}
+
 // One CTA per sequence: its last taps - 1 normalised inputs, for both sublayers.
 __global__ void __launch_bounds__(kThreads) norm_conv_state_kernel(const vila_norm_conv_params p) {
   extern __shared__ float inv_s[];   // [rows kept][groups]
@@ -222,23 +310,28 @@ __global__ void __launch_bounds__(kThreads) norm_conv_state_kernel(const vila_no
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int pair = warp; pair < keep * groups; pair += kThreads / 32) {
     const int k = pair / groups, piece = pair - k * groups;     // k-th of the kept rows: row0 + n - keep + k
-    const float r = piece_inv(p.x + static_cast<size_t>(row0 + n - keep + k) * cols + static_cast<size_t>(piece) * gc, gc, p.eps);
+    const int row = row0 + n - keep + k;
+    const float r = p.inv ? p.inv[row * groups + piece]
+                          : piece_inv(p.x + static_cast<size_t>(row) * cols + static_cast<size_t>(piece) * gc, gc, p.eps);
     if (lane == 0) inv_s[pair] = r;
   }
   __syncthreads();
   const size_t soff = static_cast<size_t>(slot) * back * cols;
-  for (int c = threadIdx.x; c < cols; c += kThreads) {
+  for (int c = blockIdx.y * kThreads + threadIdx.x; c < cols; c += gridDim.y * kThreads) {
     const int piece = c / gc;
     for (int j = 0; j < back; ++j) {
       const int q = pos0 + n - back + j;          // position held by new state row j
       const bool fresh = q >= pos0;
       const int k = j - (back - keep);            // index among the kept rows
       const float xn = fresh ? p.x[static_cast<size_t>(row0 + n - keep + k) * cols + c] * inv_s[k * groups + piece] : 0.f;
-      for (int u = 0; u < p.nsub; ++u) {
-        float v = 0.f;
-        if (fresh) v = xn * (p.norm_w[u][c] + p.w_offset);
-        else if (q >= 0) v = p.state[u][soff + static_cast<size_t>(j + n) * cols + c];
-        p.state[u][soff + static_cast<size_t>(j) * cols + c] = v;
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (u < p.nsub) {
+          float v = 0.f;
+          if (fresh) v = xn * (p.norm_w[u][c] + p.w_offset);
+          else if (q >= 0) v = p.state[u][soff + static_cast<size_t>(j + n) * cols + c];
+          p.state[u][soff + static_cast<size_t>(j) * cols + c] = v;
+        }
       }
     }
   }
@@ -279,6 +372,28 @@ int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream) {
   for (int k = 0; k < p.nsub; ++k)
     aligned = aligned && reinterpret_cast<uintptr_t>(p.norm_w[k]) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out[k]) % 16 == 0 &&
               reinterpret_cast<uintptr_t>(p.state[k]) % 16 == 0;
+  if (aligned && p.inv != nullptr && p.rows >= 256) {
+    // many rows: statistics, then channel-slice CTAs that stream a block of rows with the weights in registers
+    const int slices = (p.cols + 4 * kThreads - 1) / (4 * kThreads);
+    int rb = p.rows * slices / (2 * 148);          // about two CTAs per SM
+    rb = rb < 4 ? 4 : (rb > 32 ? 32 : rb);
+    const dim3 sgrid((p.rows + rb - 1) / rb, slices);
+    VB_CUDA(launch_serial(group_inv_kernel, dim3((p.rows * p.groups + 7) / 8), dim3(kThreads), 0, stream, p));
+#define VB_NS(T, N) VB_CUDA(launch_serial(norm_conv_slice_kernel<T, N>, sgrid, dim3(kThreads), 0, stream, p, rb))
+    if (p.nsub == 2) {
+      if (p.taps == 2) VB_NS(2, 2);
+      else if (p.taps == 3) VB_NS(3, 2);
+      else VB_NS(4, 2);
+    } else {
+      if (p.taps == 2) VB_NS(2, 1);
+      else if (p.taps == 3) VB_NS(3, 1);
+      else VB_NS(4, 1);
+    }
+#undef VB_NS
+    if (p.taps > 1 && p.nseq > 0)
+      VB_CUDA(launch_serial(norm_conv_state_kernel, dim3(p.nseq, (p.cols + kThreads - 1) / kThreads), dim3(kThreads), smem, stream, p));
+    return 0;
+  }
 #define VB_NC(T, N) VB_CUDA(launch_serial(norm_conv_rows_vec_kernel<T, N>, dim3(p.rows), dim3(kThreads), smem, stream, p))
   if (aligned && p.nsub == 2) {
     if (p.taps == 2) VB_NC(2, 2);
@@ -292,8 +407,11 @@ int norm_conv_rows(const vila_norm_conv_params& p, cudaStream_t stream) {
     VB_CUDA(launch_serial(norm_conv_rows_kernel, dim3(p.rows), dim3(kThreads), smem, stream, p));
   }
 #undef VB_NC
-  if (p.taps > 1 && p.nseq > 0)
-    VB_CUDA(launch_serial(norm_conv_state_kernel, dim3(p.nseq), dim3(kThreads), smem, stream, p));
+  if (p.taps > 1 && p.nseq > 0) {
+    vila_norm_conv_params q = p;
+    q.inv = nullptr;   // no statistics pass ran on this path: the state kernel computes its own
+    VB_CUDA(launch_serial(norm_conv_state_kernel, dim3(p.nseq, (p.cols + kThreads - 1) / kThreads), dim3(kThreads), smem, stream, q));
+  }
   return 0;
 }
 

@@ -700,6 +700,8 @@ def norm_conv_rows(x: torch.Tensor, norm_w: Sequence[torch.Tensor], conv_w: Sequ
                 tuple(st.shape[1:]) == (taps - 1, Cc)
             p.state[k] = _p(st)
     p.seqs, p.row_seq = _i32(seqs, "seqs"), _i32(row_seq, "row_seq")
+    inv = torch.empty(T, groups, dtype=torch.float32, device=x.device)
+    p.inv = _p(inv)
     p.conv_w_dtype, p.out_dtype = _dt(conv_w[0], "conv_w"), _dt(outs[0], "out")
     p.rows, p.nseq, p.cols, p.groups, p.taps, p.nsub = T, seqs.shape[0], Cc, groups, taps, nsub
     p.eps, p.w_offset = eps, w_offset
