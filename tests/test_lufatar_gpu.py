@@ -84,6 +84,11 @@ CONFIGS = {
         (att(2, 1, 8, 8, 8, 100.0, 0.35), moe(3, 1, 16, 5.0)),
         (att(1, 1, 24, 12, 12, 1000.0, 0.2), None),
     ], groups=1, taps=1, bigram=(7, 3, 2), mult=1.0),
+    # a width that is no multiple of 4 (no 16-byte rows anywhere), two taps, pieces of 14 channels
+    "narrow": config(42, 35, [
+        (att(3, 1, 14, 9, 6, 300.0, 0.3), moe(6, 3, 10, 0.5, count=2, keep=2)),
+        (att(2, 2, 5, 7, 4, 20.0, 0.45), moe(2, 1, 6, 1.0, count=2, keep=1)),
+    ], groups=3, taps=2, bigram=(19, 23, 29), mult=0.9, side=7, loop=(1, 2, 2)),
     "plain2": config(48, 50, [
         (att(2, 2, 12, 12, 6, 100.0, 0.3), moe(4, 2, 8, 1.0, count=2, keep=1)),
     ], groups=2, taps=6, bigram=(11, 13, 17), mult=0.5, side=4, loop=(0, 1, 2)),
@@ -92,6 +97,12 @@ CONFIGS = {
 
 def build(name, dtype, seed=0):
     """name: a key of CONFIGS or a configuration dictionary"""
+    if name == "narrow" and dtype == BF:
+        # heads of 5 columns and a side input of 7: when such a short vector is nearly zero, its unit norm
+        # multiplies the bf16 rounding of the projection before it, and single rows leave the tolerance
+        # (seen in about one row of 150 per model).  The narrow sizes run in fp32; bf16 on widths that are no
+        # multiple of 8 is covered by "odd" and by the kernels' own tests.
+        pytest.skip("the narrow model is compared in fp32 only")
     from vila_b200.model import LufatarConfig, LufatarForCausalLM
     cfg = CONFIGS[name] if isinstance(name, str) else name
     model = LufatarForCausalLM(LufatarConfig.from_dict(cfg), "cuda", dtype).init_random(seed, scale=1.5)
@@ -582,7 +593,7 @@ def test_whole_prompt_and_layers(cuda, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF])
-@pytest.mark.parametrize("name", ["odd", "aligned", "plain2"])
+@pytest.mark.parametrize("name", ["odd", "aligned", "plain2", "narrow"])
 def test_decode_and_portions_match_whole(cuda, name, dtype):
     cfg, model = build(name, dtype, seed=3)
     prompts = {"p": tokens_for(cfg, 140, 2)}
